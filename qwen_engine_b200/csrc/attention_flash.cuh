@@ -7,7 +7,8 @@
 // in tiles of 64 through a two-stage cp.async pipeline, gathered page by page from the block table.
 // Scores, running max, running sum and the output accumulator are float32; P is rounded to
 // bfloat16 before P·V (attn.py:263); the mask is key <= position (and > position - window)
-// (attn.py:195, 239).  Tiles above the causal frontier are never visited.
+// (attn.py:195, 239).  Tiles above the causal frontier are never visited.  A mixer may bias the scores by
+// distance: slopes[head] * (position - key) is then taken off each score (float32, before the softmax).
 //
 // A work item may cover only a range of keys (a split of a long context for a decoded token:
 // flash decoding, attn.py:374-594 with split_size 256); then it writes its unnormalised
@@ -62,11 +63,14 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // of 16 keys starting at block kb0 of the tile.  Updates the rows' running max, sum and output.
 // `all_allowed`: every key of the tile is allowed for every row of the warp (a tile below the causal
 // diagonal, inside the key range and the window): the mask is skipped (uniform over the warp).
-template <int D, int NB>
+// BIAS: slope_lo / slope_hi (in units of log2 e, like the scale) times the distance position - key is taken
+// off the scores of the thread's two rows.
+template <int D, int NB, bool BIAS = false>
 __device__ __forceinline__ void fa_tile(const __nv_bfloat16* sq, const __nv_bfloat16* tk, const __nv_bfloat16* tv,
                                         int row_base, int kb0, int kt, int kv_begin, int kv_end, int pos_lo, int pos_hi,
                                         int window, float scale_log2, int lane, float& m_lo, float& m_hi, float& l_lo,
-                                        float& l_hi, float (&o)[D / 8][4], bool all_allowed) {
+                                        float& l_hi, float (&o)[D / 8][4], bool all_allowed,
+                                        float slope_lo = 0.f, float slope_hi = 0.f) {
   constexpr int LD = D + 8, KS = D / 16;
   const int c = lane & 3;
   // ---- S = Q K^T ---------------------------------------------------------------------------
@@ -96,6 +100,11 @@ __device__ __forceinline__ void fa_tile(const __nv_bfloat16* sq, const __nv_bflo
       for (int e = 0; e < 2; ++e) {
         s[i][e] *= scale_log2;
         s[i][2 + e] *= scale_log2;
+        if (BIAS) {
+          const int key = kt + kb0 * 16 + i * 8 + 2 * c + e;
+          s[i][e] = fmaf(-slope_lo, (float)(pos_lo - key), s[i][e]);
+          s[i][2 + e] = fmaf(-slope_hi, (float)(pos_hi - key), s[i][2 + e]);
+        }
         mx_lo = fmaxf(mx_lo, s[i][e]);
         mx_hi = fmaxf(mx_hi, s[i][2 + e]);
       }
@@ -109,8 +118,8 @@ __device__ __forceinline__ void fa_tile(const __nv_bfloat16* sq, const __nv_bflo
       const bool in_range = key >= kv_begin && key < kv_end;
       const bool ok_lo = in_range && key <= pos_lo && (window <= 0 || key > pos_lo - window);
       const bool ok_hi = in_range && key <= pos_hi && (window <= 0 || key > pos_hi - window);
-      s[i][e] = ok_lo ? s[i][e] * scale_log2 : -INFINITY;
-      s[i][2 + e] = ok_hi ? s[i][2 + e] * scale_log2 : -INFINITY;
+      s[i][e] = ok_lo ? (BIAS ? fmaf(-slope_lo, (float)(pos_lo - key), s[i][e] * scale_log2) : s[i][e] * scale_log2) : -INFINITY;
+      s[i][2 + e] = ok_hi ? (BIAS ? fmaf(-slope_hi, (float)(pos_hi - key), s[i][2 + e] * scale_log2) : s[i][2 + e] * scale_log2) : -INFINITY;
       mx_lo = fmaxf(mx_lo, s[i][e]);
       mx_hi = fmaxf(mx_hi, s[i][2 + e]);
     }
@@ -250,6 +259,7 @@ struct FaArgs {
   const int* items; __nv_bfloat16* out;
   float* part_acc; float* part_ml; int part_rows;
   int* counters; float scale_log2; int window, Hq, Hkv, page_size;
+  const float* slopes;      // null, or float32 [Hq]: slopes[h] * (position - key) is taken off the score (last: may be left out)
 };
 
 // The work of one CTA (work item `item_idx`, kv head `hkv`) by 256 threads; `smem_raw`: the dynamic
@@ -385,6 +395,10 @@ __device__ __forceinline__ void flash_attention_cta(const FaArgs& A, int item_id
   const int r_lo = row_base + g, r_hi = r_lo + 8;
   const int pos_lo = r_lo < nrows ? first_pos + r_lo / G : -1;             // -1: the row is padding
   const int pos_hi = r_hi < nrows ? first_pos + r_hi / G : -1;
+  // the distance bias of the rows' heads (row r is head hkv * G + r % G), in units of log2 e like the scale
+  const bool biased = A.slopes != nullptr;
+  const float slope_lo = biased && r_lo < nrows ? A.slopes[hkv * G + r_lo % G] * 1.4426950408889634f : 0.f;
+  const float slope_hi = biased && r_hi < nrows ? A.slopes[hkv * G + r_hi % G] * 1.4426950408889634f : 0.f;
   float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
   float o[D / 8][4];
 #pragma unroll
@@ -406,7 +420,14 @@ __device__ __forceinline__ void flash_attention_cta(const FaArgs& A, int item_id
       const int pos_first = first_pos + row_first / G, pos_last = first_pos + row_last / G;
       const bool all_allowed = row_base + 16 <= nrows && kt >= kv_begin && kt + FA_BN <= kv_end &&
                                kt + FA_BN - 1 <= pos_first && (window <= 0 || kt > pos_last - window);
-      if (keysplit)
+      if (biased) {
+        if (keysplit)
+          fa_tile<D, 1, true>(sq, tk, tv, 0, warp, kt, kv_begin, kv_end, pos_lo, pos_hi, window, scale_log2, lane,
+                              m_lo, m_hi, l_lo, l_hi, o, false, slope_lo, slope_hi);
+        else
+          fa_tile<D, FA_BN / 16, true>(sq, tk, tv, row_base, 0, kt, kv_begin, kv_end, pos_lo, pos_hi, window, scale_log2,
+                                       lane, m_lo, m_hi, l_lo, l_hi, o, all_allowed, slope_lo, slope_hi);
+      } else if (keysplit)
         fa_tile<D, 1>(sq, tk, tv, 0, warp, kt, kv_begin, kv_end, pos_lo, pos_hi, window, scale_log2, lane,
                       m_lo, m_hi, l_lo, l_hi, o, false);
       else

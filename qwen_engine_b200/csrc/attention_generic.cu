@@ -3,7 +3,8 @@
 // groups, float32 or bfloat16 storage; all arithmetic in float32 with expf.
 //
 // For the query at position i of a request, key j is allowed iff j <= i and (window == 0 or
-// j > i - window) (reference src/layers/fused_ops/attn.py:195, 239); scores are scale * q·k,
+// j > i - window) (reference src/layers/fused_ops/attn.py:195, 239); scores are scale * q·k, less
+// slopes[head] * (i - j) where a mixer biases by distance,
 // softmax runs online over key tiles of 32 that start at multiples of 32 of the absolute key
 // position, so the order of a query's reduction does not depend on how the request was cut into
 // steps (attn.py:236-267 has the same algebra per BLOCK_N).  Query head h reads kv head
@@ -25,7 +26,7 @@ attention_generic_kernel(const T* __restrict__ q, long q_stride, const T* __rest
                          const int* __restrict__ block_tables, int max_blocks,
                          const int* __restrict__ cu_q, const int* __restrict__ ctx_lens,
                          const int* __restrict__ tiles, T* __restrict__ out, float scale, int window,
-                         int Hq, int Hkv, int D, int page_size) {
+                         int Hq, int Hkv, int D, int page_size, const float* __restrict__ slopes) {
   extern __shared__ float smem[];
   pdl_launch_dependents();
   pdl_wait();
@@ -35,6 +36,7 @@ attention_generic_kernel(const T* __restrict__ q, long q_stride, const T* __rest
   float* vs = ks + AG_BN * Dp;                // [AG_BN][D]
   const int tile = blockIdx.x, hq = blockIdx.y;
   const int hkv = hq / (Hq / Hkv);
+  const float slope = slopes ? slopes[hq] : 0.f;        // distance bias: slope * (i - j) is taken off the score
   const int req = tiles[2 * tile], q0 = tiles[2 * tile + 1];
   const int row0 = cu_q[req];
   const int q_len = cu_q[req + 1] - row0;
@@ -90,7 +92,7 @@ attention_generic_kernel(const T* __restrict__ q, long q_stride, const T* __rest
       const float* qr = qs + r * D;
       const float* kr = ks + lane * Dp;
       for (int d = 0; d < D; ++d) s = fmaf(qr[d], kr[d], s);
-      s = ok ? s * scale : -INFINITY;
+      s = ok ? fmaf(-slope, (float)(pos - kj), s * scale) : -INFINITY;
       const float tile_max = warp_max(s);
       if (tile_max == -INFINITY) continue;              // nothing allowed in this tile
       const float m_new = fmaxf(m[i], tile_max);
@@ -128,7 +130,7 @@ extern "C" int qe_paged_attention_generic(const void* q, long q_stride, const vo
                                           const int* block_tables, int max_blocks, const int* cu_q,
                                           const int* ctx_lens, const int* tiles, int n_tiles, void* out,
                                           float scale, int window, int Hq, int Hkv, int D, int page_size,
-                                          int dtype, cudaStream_t stream) {
+                                          int dtype, const float* slopes, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (D > AG_MAX_D || D < 1) QE_REFUSE("paged_attention: head_dim %d is outside 1..%d", D, AG_MAX_D);
   if (Hkv < 1 || Hq % Hkv) QE_REFUSE("paged_attention: %d query heads do not group over %d kv heads", Hq, Hkv);
@@ -147,11 +149,11 @@ extern "C" int qe_paged_attention_generic(const void* q, long q_stride, const vo
   if (dtype == QE_DTYPE_F32) {
     qe_launch(attention_generic_kernel<float>, grid, dim3(AG_WARPS * 32), smem, stream,
         (const float*)q, q_stride, (const float*)pages, block_tables, max_blocks, cu_q, ctx_lens, tiles,
-        (float*)out, scale, window, Hq, Hkv, D, page_size);
+        (float*)out, scale, window, Hq, Hkv, D, page_size, slopes);
   } else if (dtype == QE_DTYPE_BF16) {
     qe_launch(attention_generic_kernel<__nv_bfloat16>, grid, dim3(AG_WARPS * 32), smem, stream,
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)pages, block_tables, max_blocks, cu_q, ctx_lens,
-        tiles, (__nv_bfloat16*)out, scale, window, Hq, Hkv, D, page_size);
+        tiles, (__nv_bfloat16*)out, scale, window, Hq, Hkv, D, page_size, slopes);
   } else QE_REFUSE("paged_attention: unknown dtype %d", dtype);
   QE_CHECK_LAUNCH("paged_attention_generic");
   return 0;

@@ -6,12 +6,14 @@
 #include "rope_d128.cuh"
 
 // ---------------------------------------------------------------------------------------
-// out[t, :] = float(table[ids[t], :])      (reference src/layers/ops/embedding.py:28-44)
+// out[t, :] = float(table[ids[t], :]) * scale   (reference src/layers/ops/embedding.py:28-44; scale 1 there),
+// or, with `accumulate`, out[t, :] += that (a pass that starts again from the tokens).
 // The residual stream is float32 in both paths.  An id outside the table gives NaN rows.
 // ---------------------------------------------------------------------------------------
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
-                                 float* __restrict__ out, int H, int V, float* __restrict__ ssq_out, int ssq_ld) {
+                                 float* __restrict__ out, int H, int V, float* __restrict__ ssq_out, int ssq_ld,
+                                 float scale, int accumulate) {
   __shared__ float scratch[33];
   const int t = blockIdx.x;
   pdl_launch_dependents();
@@ -26,7 +28,11 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
   }
   const T* src = table + (size_t)id * H;
   float ss = 0.f;
-  for (int h = threadIdx.x; h < H; h += blockDim.x) { const float v = to_f32(src[h]); dst[h] = v; ss += v * v; }
+  if (accumulate) {                                // the row times `scale` is added to what the stream holds
+    for (int h = threadIdx.x; h < H; h += blockDim.x) dst[h] += to_f32(src[h]) * scale;
+    return;
+  }
+  for (int h = threadIdx.x; h < H; h += blockDim.x) { const float v = to_f32(src[h]) * scale; dst[h] = v; ss += v * v; }
   if (ssq_out) {                                   // the row's sum of squares, for a norm fused downstream
     ss = block_sum(ss, scratch);
     if (threadIdx.x == 0) ssq_out[(size_t)t * ssq_ld] = ss;
@@ -34,12 +40,15 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
 }
 
 extern "C" int qe_embedding(const int* ids, const void* table, float* out, int T, int H, int V,
-                            int dtype, float* ssq_out, int ssq_ld, cudaStream_t stream) {
+                            int dtype, float* ssq_out, int ssq_ld, float scale, int accumulate, cudaStream_t stream) {
   if (T <= 0) return 0;
+  if (accumulate) ssq_out = nullptr;
   if (dtype == QE_DTYPE_F32)
-    qe_launch(embedding_kernel<float>, dim3(T), dim3(256), 0, stream, ids, (const float*)table, out, H, V, ssq_out, ssq_ld);
+    qe_launch(embedding_kernel<float>, dim3(T), dim3(256), 0, stream, ids, (const float*)table, out, H, V, ssq_out, ssq_ld,
+              scale, accumulate);
   else if (dtype == QE_DTYPE_BF16)
-    qe_launch(embedding_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, ids, (const __nv_bfloat16*)table, out, H, V, ssq_out, ssq_ld);
+    qe_launch(embedding_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, ids, (const __nv_bfloat16*)table, out, H, V, ssq_out,
+              ssq_ld, scale, accumulate);
   else QE_REFUSE("embedding: unknown dtype %d", dtype);
   QE_CHECK_LAUNCH("embedding");
   return 0;
@@ -252,8 +261,14 @@ extern "C" int qe_add_rmsnorm(float* resid, const void* delta, const int* rows, 
 // out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i],  silu(g) = g / (1 + exp(-g))
 // (reference src/layers/fused_ops/silumul.py:50-53), all in float32, rounded once.
 // ---------------------------------------------------------------------------------------
+// act: 0 silu; 1 the tanh form of gelu, 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3)))
+__device__ __forceinline__ float gate_act(float g, int act) {
+  if (act == 1) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+  return g / (1.f + expf(-g));
+}
+
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int I, size_t total) {
+__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int I, size_t total, int act) {
   pdl_launch_dependents();
   pdl_wait();
   for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
@@ -261,7 +276,7 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
     const int i = (int)(e - t * I);
     const float g = to_f32(gate_up[t * 2 * I + i]);
     const float u = to_f32(gate_up[t * 2 * I + I + i]);
-    out[e] = from_f32<T>(g / (1.f + expf(-g)) * u);
+    out[e] = from_f32<T>(gate_act(g, act) * u);
   }
 }
 
@@ -298,10 +313,18 @@ __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up
   }
 }
 
+static int act_mul_launch(const void* gate_up, void* out, int T, int I, int dtype, int act, cudaStream_t stream);
 extern "C" int qe_silu_mul(const void* gate_up, void* out, int T, int I, int dtype, cudaStream_t stream) {
+  return act_mul_launch(gate_up, out, T, I, dtype, 0, stream);
+}
+extern "C" int qe_act_mul(const void* gate_up, void* out, int T, int I, int dtype, int act, cudaStream_t stream) {
+  if (act < 0 || act > 1) QE_REFUSE("act_mul: unknown activation %d", act);
+  return act_mul_launch(gate_up, out, T, I, dtype, act, stream);
+}
+static int act_mul_launch(const void* gate_up, void* out, int T, int I, int dtype, int act, cudaStream_t stream) {
   if (T <= 0) return 0;
   const size_t total = (size_t)T * I;
-  if (dtype == QE_DTYPE_BF16 && I % 8 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0) {
+  if (act == 0 && dtype == QE_DTYPE_BF16 && I % 8 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0) {
     const size_t total8 = total / 8;
     const int vblocks = (int)((total8 + 255) / 256 < 148 * 8 ? (total8 + 255) / 256 : 148 * 8);
     qe_launch(silu_mul_bf16x8_kernel, dim3(vblocks), dim3(256), 0, stream, (const __nv_bfloat16*)gate_up,
@@ -312,9 +335,9 @@ extern "C" int qe_silu_mul(const void* gate_up, void* out, int T, int I, int dty
   const int threads = 256;
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
   if (dtype == QE_DTYPE_F32)
-    qe_launch(silu_mul_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float*)gate_up, (float*)out, I, total);
+    qe_launch(silu_mul_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float*)gate_up, (float*)out, I, total, act);
   else if (dtype == QE_DTYPE_BF16)
-    qe_launch(silu_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, I, total);
+    qe_launch(silu_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, I, total, act);
   else QE_REFUSE("silu_mul: unknown dtype %d", dtype);
   QE_CHECK_LAUNCH("silu_mul");
   return 0;
@@ -335,7 +358,7 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ q, T* __restrict__ 
                                              const float* __restrict__ qw, const float* __restrict__ kw, float eps,
                                              const float* __restrict__ inv_freq, int rotary_dim,
                                              T* __restrict__ pages, const int* __restrict__ slot_mapping,
-                                             int T_tokens, int Hq, int Hkv, int D, int page_size, int write_kv) {
+                                             int T_tokens, int Hq, int Hkv, int D, int page_size, int write_kv, int norm_dim) {
   extern __shared__ float smem[];
   pdl_launch_dependents();
   pdl_wait();
@@ -370,7 +393,7 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ q, T* __restrict__ 
   }
   if (w) {
     ss = warp_sum(ss);
-    const float rstd = rsqrtf(ss / (float)D + eps);
+    const float rstd = rsqrtf(ss / (float)norm_dim + eps);     // (a head padded with zero channels is normed over its own)
     for (int d = lane; d < D; d += 32) buf[d] = buf[d] * rstd * w[d];
   }
   __syncwarp();
@@ -455,13 +478,14 @@ extern "C" int qe_qk_norm_rope_kv_write(void* q, void* k, const void* v, long q_
                                         const int* positions, const float* qw, const float* kw, float eps,
                                         const float* inv_freq, const void* cos_sin, int rotary_dim, void* pages,
                                         const int* slot_mapping, int T, int Hq, int Hkv, int D, int page_size,
-                                        int write_kv, int dtype, cudaStream_t stream) {
+                                        int write_kv, int dtype, int norm_dim, cudaStream_t stream) {
   if (T <= 0) return 0;
+  if (norm_dim <= 0) norm_dim = D;
   if (D > QKR_MAX_D) QE_REFUSE("qk_norm_rope_kv_write: head_dim %d is above %d", D, QKR_MAX_D);
   if (inv_freq && (rotary_dim % 2 || rotary_dim > D || rotary_dim <= 0))
     QE_REFUSE("qk_norm_rope_kv_write: rotary_dim %d does not fit head_dim %d", rotary_dim, D);
   if (write_kv && (!pages || !slot_mapping)) QE_REFUSE("qk_norm_rope_kv_write: cache write without cache");
-  if (dtype == QE_DTYPE_BF16 && D == 128 && (!inv_freq || rotary_dim == D) &&
+  if (dtype == QE_DTYPE_BF16 && D == 128 && norm_dim == D && (!inv_freq || rotary_dim == D) &&
       ((q_stride | k_stride | v_stride) % 4) == 0 &&
       (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)pages) & 7) == 0) {
     const long n_items = (long)T * (Hq + 2 * Hkv);
@@ -485,11 +509,11 @@ extern "C" int qe_qk_norm_rope_kv_write(void* q, void* k, const void* v, long q_
   if (dtype == QE_DTYPE_F32)
     qe_launch(qk_norm_rope_kv_write_kernel<float>, dim3(blocks), dim3(warps * 32), smem, stream,
         (float*)q, (float*)k, (const float*)v, q_stride, k_stride, v_stride, positions, qw, kw, eps, inv_freq,
-        rotary_dim, (float*)pages, slot_mapping, T, Hq, Hkv, D, page_size, write_kv);
+        rotary_dim, (float*)pages, slot_mapping, T, Hq, Hkv, D, page_size, write_kv, norm_dim);
   else if (dtype == QE_DTYPE_BF16)
     qe_launch(qk_norm_rope_kv_write_kernel<__nv_bfloat16>, dim3(blocks), dim3(warps * 32), smem, stream,
         (__nv_bfloat16*)q, (__nv_bfloat16*)k, (const __nv_bfloat16*)v, q_stride, k_stride, v_stride, positions, qw, kw,
-        eps, inv_freq, rotary_dim, (__nv_bfloat16*)pages, slot_mapping, T, Hq, Hkv, D, page_size, write_kv);
+        eps, inv_freq, rotary_dim, (__nv_bfloat16*)pages, slot_mapping, T, Hq, Hkv, D, page_size, write_kv, norm_dim);
   else QE_REFUSE("qk_norm_rope_kv_write: unknown dtype %d", dtype);
   QE_CHECK_LAUNCH("qk_norm_rope_kv_write");
   return 0;

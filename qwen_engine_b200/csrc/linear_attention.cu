@@ -1,0 +1,370 @@
+// Gated linear attention with a decay per key channel, as a recurrence over tokens with its state in
+// float32, for any mixture of prompt portions and single decoded tokens:
+//
+//   S_t = diag(alpha_t) S_(t-1) + k_t v_t^T        (S: key channels x value channels, one per head and request)
+//   o_t = S_t^T (q_scale q_t)
+//
+// and the two small kernels around it: the decay alpha = sigmoid(z)^(1/tau) from a low-rank projection, and
+// the per-head RMS norm of o with an output gate.  Everything that enters the recurrence besides q, k, v is
+// float32 (z, its log-sigmoid, alpha, the state, o); q, k, v come in the step's compute type.
+//
+// The scan: one CTA per (request, head, tile of value channels).  A value channel's column of S evolves on
+// its own, so the columns are dealt to threads: thread (j, l) keeps DC consecutive key channels of column j
+// in registers (L = threads per column, L * DC >= key channels), multiplies, adds and reduces over l by
+// shuffles; the order of every sum is fixed by the sizes alone, so a token's output does not depend on how
+// the request was cut into steps or on what else the step carries.  Four producer warps stage the next
+// chunk of tokens (q scaled, k, alpha, v, as float32) in shared memory while the others compute.
+// State in memory: [slot][head][value channel][key channel] float32; a request whose context is empty
+// starts from zero whatever its slot holds.
+#include "common.cuh"
+#include <math.h>
+
+// ---------------------------------------------------------------------------------------------------------
+// alpha[t, n] = exp(logsigmoid(z) / tau),  z = sum_r a[t, r] w[n, r] + bias[n]
+// ---------------------------------------------------------------------------------------------------------
+#define DEC_COLS 128
+#define DEC_ROWS 16
+template <typename T>
+__global__ void __launch_bounds__(DEC_COLS)
+channel_decay_kernel(const T* __restrict__ a, long lda, const T* __restrict__ w, const float* __restrict__ bias,
+                     float inv_tau, float* __restrict__ out, int T_tokens, int N, int R) {
+  extern __shared__ float smem[];
+  float* ws = smem;                          // [DEC_COLS][R + 1]
+  float* as = ws + DEC_COLS * (R + 1);       // [DEC_ROWS][R]
+  const int n0 = blockIdx.x * DEC_COLS, t0 = blockIdx.y * DEC_ROWS;
+  pdl_launch_dependents();
+  for (int e = threadIdx.x; e < DEC_COLS * R; e += blockDim.x) {       // weights: nothing of the step writes them
+    const int n = e / R, r = e - n * R;
+    ws[n * (R + 1) + r] = n0 + n < N ? to_f32(w[(size_t)(n0 + n) * R + r]) : 0.f;
+  }
+  pdl_wait();
+  const int rows = min(DEC_ROWS, T_tokens - t0);
+  for (int e = threadIdx.x; e < rows * R; e += blockDim.x) {
+    const int t = e / R, r = e - t * R;
+    as[e] = to_f32(a[(size_t)(t0 + t) * lda + r]);
+  }
+  __syncthreads();
+  const int n = n0 + threadIdx.x;
+  if (n >= N) return;
+  const float b = bias ? bias[n] : 0.f;
+  const float* wr = ws + threadIdx.x * (R + 1);
+  for (int t = 0; t < rows; ++t) {
+    float z = b;
+    const float* ar = as + t * R;
+    for (int r = 0; r < R; ++r) z = fmaf(ar[r], wr[r], z);
+    const float logsig = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
+    out[(size_t)(t0 + t) * N + n] = expf(logsig * inv_tau);
+  }
+}
+
+extern "C" int qe_channel_decay(const void* a, long lda, const void* w, const float* bias, float tau, float* out,
+                                int T, int N, int R, int dtype, cudaStream_t stream) {
+  if (T <= 0 || N <= 0) return 0;
+  if (R < 1 || R > 256) QE_REFUSE("channel_decay: rank %d is outside 1..256", R);
+  if (!(tau > 0.f)) QE_REFUSE("channel_decay: tau must be positive");
+  const size_t smem = ((size_t)DEC_COLS * (R + 1) + (size_t)DEC_ROWS * R) * sizeof(float);
+  static bool configured = false;
+  if (!configured) {
+    const int max_smem = (int)(((size_t)DEC_COLS * 257 + (size_t)DEC_ROWS * 256) * sizeof(float));
+    cudaError_t e = cudaFuncSetAttribute(channel_decay_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(channel_decay_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    if (e != cudaSuccess) QE_REFUSE("channel_decay: shared memory %d: %s", max_smem, cudaGetErrorString(e));
+    configured = true;
+  }
+  dim3 grid((N + DEC_COLS - 1) / DEC_COLS, (T + DEC_ROWS - 1) / DEC_ROWS);
+  if (dtype == QE_DTYPE_F32)
+    qe_launch(channel_decay_kernel<float>, grid, dim3(DEC_COLS), smem, stream, (const float*)a, lda, (const float*)w, bias,
+              1.f / tau, out, T, N, R);
+  else if (dtype == QE_DTYPE_BF16)
+    qe_launch(channel_decay_kernel<__nv_bfloat16>, grid, dim3(DEC_COLS), smem, stream, (const __nv_bfloat16*)a, lda,
+              (const __nv_bfloat16*)w, bias, 1.f / tau, out, T, N, R);
+  else QE_REFUSE("channel_decay: unknown dtype %d", dtype);
+  QE_CHECK_LAUNCH("channel_decay");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// the scan
+// ---------------------------------------------------------------------------------------------------------
+#define GLA_PRODUCERS 128          // threads that stage the next chunk
+#define GLA_MAX_COMPUTE 256        // threads that hold state
+
+struct GlaArgs {
+  const void* q; const void* k; const void* v;        // rows of the step's tokens; heads side by side
+  long ldq, ldk, ldv;                                 // row strides in elements
+  const float* alpha;                                 // [T, H * dk]
+  float* state;                                       // [slots, H, dv, dk]
+  const int* cu_q; const int* ctx_lens; const int* slot_ids;
+  float* out;                                         // [T, H * dv]
+  float q_scale;
+  int H, dk, dv, L, VT, chunk, write_state;
+};
+
+// index of key channel c in a staged row: blocks of DC channels, 4 floats of padding between them (banks)
+template <int DC> __device__ __forceinline__ int gla_pad(int c) { return c + (c / DC) * 4; }
+
+template <typename T, int DC>
+__global__ void __launch_bounds__(GLA_MAX_COMPUTE + GLA_PRODUCERS)
+gla_scan_kernel(GlaArgs A) {
+  extern __shared__ float smem[];
+  const int req = blockIdx.x, head = blockIdx.y, j0 = blockIdx.z * A.VT;
+  const int dk = A.dk, dv = A.dv, L = A.L, VT = A.VT, H = A.H;
+  const int n_compute = VT * L;
+  const int row_w = gla_pad<DC>(L * DC);               // floats of one staged row of q, k or alpha
+  const int tok_w = 3 * row_w + ((VT + 3) & ~3);       // floats of one staged token (rows stay 16-byte aligned)
+  float* buf[2] = {smem, smem + (size_t)A.chunk * tok_w};
+  const bool producer = threadIdx.x >= n_compute;
+  const int tid = threadIdx.x;
+  const int j = j0 + tid / L, l = tid % L;
+  const bool owns = !producer && j < dv;
+  // the L threads of a column are neighbours within one warp; only they meet in the shuffles
+  const unsigned col_mask = L >= 32 ? 0xffffffffu : (((1u << L) - 1u) << ((threadIdx.x & 31) & ~(L - 1)));
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row0 = A.cu_q[req];
+  const int n = A.cu_q[req + 1] - row0;
+  if (n <= 0) return;
+  const int ctx = A.ctx_lens[req];
+  const int slot = A.slot_ids[req];
+  float* st = A.state + (((size_t)slot * H + head) * dv + (owns ? j : 0)) * dk;
+
+  float s[DC];
+#pragma unroll
+  for (int i = 0; i < DC; ++i) s[i] = 0.f;
+  if (owns && ctx > 0) {
+    if (dk % 4 == 0) {
+#pragma unroll
+      for (int i = 0; i < DC; i += 4) {
+        const int c = l * DC + i;
+        if (c < dk) { const float4 x = *reinterpret_cast<const float4*>(st + c); s[i] = x.x; s[i + 1] = x.y; s[i + 2] = x.z; s[i + 3] = x.w; }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < DC; ++i) { const int c = l * DC + i; if (c < dk) s[i] = st[c]; }
+    }
+  }
+
+  const T* q = (const T*)A.q + (size_t)head * dk;
+  const T* k = (const T*)A.k + (size_t)head * dk;
+  const T* v = (const T*)A.v + (size_t)head * dv;
+  const float* al = A.alpha + (size_t)head * dk;
+  const int n_chunks = (n + A.chunk - 1) / A.chunk;
+  const int ptid = tid - n_compute, n_prod = blockDim.x - n_compute;
+  const int padded = L * DC;
+
+  // stage chunk `ch` into buf[ch & 1]: by the producers, or by everybody for the first chunk
+  auto stage = [&](int ch, int t_id, int t_n) {
+    float* b = buf[ch & 1];
+    const int t_first = ch * A.chunk;
+    const int rows = min(A.chunk, n - t_first);
+    const int per_tok = 3 * padded + VT;
+    for (int e = t_id; e < rows * per_tok; e += t_n) {
+      const int t = e / per_tok, x = e - t * per_tok;
+      const size_t row = (size_t)(row0 + t_first + t);
+      float* dst = b + (size_t)t * tok_w;
+      if (x < 3 * padded) {
+        const int which = x / padded, c = x - which * padded;
+        float val;
+        if (c >= dk) val = which == 2 ? 1.f : 0.f;                     // channels beyond the head: nothing in, nothing out
+        else if (which == 0) val = to_f32(q[row * A.ldq + c]) * A.q_scale;
+        else if (which == 1) val = to_f32(k[row * A.ldk + c]);
+        else val = al[row * ((size_t)H * dk) + c];
+        dst[which * row_w + gla_pad<DC>(c)] = val;
+      } else {
+        const int jj = x - 3 * padded;
+        dst[3 * row_w + jj] = j0 + jj < dv ? to_f32(v[row * A.ldv + j0 + jj]) : 0.f;
+      }
+    }
+  };
+
+  stage(0, tid, blockDim.x);
+  __syncthreads();
+  for (int ch = 0; ch < n_chunks; ++ch) {
+    if (producer) {
+      if (ch + 1 < n_chunks) stage(ch + 1, ptid, n_prod);
+    } else if (owns) {
+      const float* b = buf[ch & 1];
+      const int rows = min(A.chunk, n - ch * A.chunk);
+      float* o = A.out + (size_t)(row0 + ch * A.chunk) * ((size_t)H * dv) + (size_t)head * dv + j;
+      for (int t = 0; t < rows; ++t) {
+        const float* r = b + (size_t)t * tok_w;
+        const float* rq = r + l * (DC + 4);
+        const float* rk = rq + row_w;
+        const float* ra = rk + row_w;
+        const float vj = r[3 * row_w + (j - j0)];
+        float acc = 0.f;
+#pragma unroll
+        for (int i = 0; i < DC; i += 4) {
+          const float4 q4 = *reinterpret_cast<const float4*>(rq + i);
+          const float4 k4 = *reinterpret_cast<const float4*>(rk + i);
+          const float4 a4 = *reinterpret_cast<const float4*>(ra + i);
+          s[i] = fmaf(a4.x, s[i], k4.x * vj);             acc = fmaf(q4.x, s[i], acc);
+          s[i + 1] = fmaf(a4.y, s[i + 1], k4.y * vj);     acc = fmaf(q4.y, s[i + 1], acc);
+          s[i + 2] = fmaf(a4.z, s[i + 2], k4.z * vj);     acc = fmaf(q4.z, s[i + 2], acc);
+          s[i + 3] = fmaf(a4.w, s[i + 3], k4.w * vj);     acc = fmaf(q4.w, s[i + 3], acc);
+        }
+        for (int off = L >> 1; off > 0; off >>= 1) acc += __shfl_xor_sync(col_mask, acc, off);
+        if (l == 0) o[(size_t)t * ((size_t)H * dv)] = acc;
+      }
+    }
+    __syncthreads();
+  }
+  if (owns && A.write_state) {
+    if (dk % 4 == 0) {
+#pragma unroll
+      for (int i = 0; i < DC; i += 4) {
+        const int c = l * DC + i;
+        if (c < dk) *reinterpret_cast<float4*>(st + c) = make_float4(s[i], s[i + 1], s[i + 2], s[i + 3]);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < DC; ++i) { const int c = l * DC + i; if (c < dk) st[c] = s[i]; }
+    }
+  }
+}
+
+template <typename T, int DC>
+static int gla_launch(const GlaArgs& A, int R, cudaStream_t stream, size_t smem) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gla_scan_kernel<T, DC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    if (e != cudaSuccess) QE_REFUSE("linear_attention_scan: shared memory: %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  const int n_compute = A.VT * A.L;
+  const int threads = ((n_compute + 31) / 32) * 32 + GLA_PRODUCERS;
+  dim3 grid(R, A.H, (A.dv + A.VT - 1) / A.VT);
+  qe_launch(gla_scan_kernel<T, DC>, grid, dim3(threads), smem, stream, A);
+  QE_CHECK_LAUNCH("linear_attention_scan");
+  return 0;
+}
+
+// How the key channels of a head are dealt to threads: DC channels a thread, L threads a column.
+static void gla_shape(int dk, int* DC, int* L) {
+  int dc = dk <= 16 ? 4 : dk <= 64 ? 8 : dk <= 128 ? 16 : 32;
+  int l = 1;
+  while (l * dc < dk) l <<= 1;
+  *DC = dc; *L = l;
+}
+
+extern "C" int qe_linear_attention_scan(const void* q, const void* k, const void* v, long ldq, long ldk, long ldv,
+                                        const float* alpha, float* state, const int* cu_q, const int* ctx_lens,
+                                        const int* slot_ids, float* out, float q_scale, int R, int max_q_len, int H,
+                                        int dk, int dv, int write_state, int dtype, cudaStream_t stream) {
+  if (R <= 0) return 0;
+  if (dk < 1 || dk > 1024 || dv < 1) QE_REFUSE("linear_attention_scan: key size %d must be 1..1024, value size %d positive", dk, dv);
+  if (H < 1 || H > 65535) QE_REFUSE("linear_attention_scan: %d heads", H);
+  int DC, L;
+  gla_shape(dk, &DC, &L);
+  if (L > 32) QE_REFUSE("linear_attention_scan: key size %d is too large", dk);
+  GlaArgs A;
+  A.q = q; A.k = k; A.v = v; A.ldq = ldq; A.ldk = ldk; A.ldv = ldv; A.alpha = alpha; A.state = state;
+  A.cu_q = cu_q; A.ctx_lens = ctx_lens; A.slot_ids = slot_ids; A.out = out; A.q_scale = q_scale;
+  A.H = H; A.dk = dk; A.dv = dv; A.L = L; A.write_state = write_state;
+  // a column's threads lie within one warp (L divides 32); a tile of value channels fills up to 256 threads,
+  // and is narrower where few requests would leave SMs idle
+  int VT = GLA_MAX_COMPUTE / L;
+  if (VT > dv) VT = dv;
+  while (VT > 8 && (long)R * H * ((dv + VT - 1) / VT) < 296 && VT * L > 64) VT = (VT + 1) / 2;
+  A.VT = VT;
+  const int row_w = L * DC + ((L * DC) / DC) * 4;
+  const int tok_w = 3 * row_w + ((VT + 3) & ~3);
+  int chunk = max_q_len < 16 ? (max_q_len < 1 ? 1 : max_q_len) : 16;
+  while (chunk > 1 && (size_t)2 * chunk * tok_w * sizeof(float) > 96 * 1024) chunk >>= 1;
+  A.chunk = chunk;
+  const size_t smem = (size_t)2 * chunk * tok_w * sizeof(float);
+  if (smem > 96 * 1024) QE_REFUSE("linear_attention_scan: key size %d needs %zu bytes of shared memory", dk, smem);
+#define GLA_CASE(TT, DCC) return gla_launch<TT, DCC>(A, R, stream, smem)
+  if (dtype == QE_DTYPE_F32) {
+    switch (DC) { case 4: GLA_CASE(float, 4); case 8: GLA_CASE(float, 8); case 16: GLA_CASE(float, 16); default: GLA_CASE(float, 32); }
+  } else if (dtype == QE_DTYPE_BF16) {
+    switch (DC) { case 4: GLA_CASE(__nv_bfloat16, 4); case 8: GLA_CASE(__nv_bfloat16, 8); case 16: GLA_CASE(__nv_bfloat16, 16);
+                  default: GLA_CASE(__nv_bfloat16, 32); }
+  }
+#undef GLA_CASE
+  QE_REFUSE("linear_attention_scan: unknown dtype %d", dtype);
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// out[t, h, j] = o[t, h, j] * rsqrt(mean_j o[t, h, :]^2 + eps) * w[j] * gate(g[t, h, j]) * scale
+// o float32 [T, H * D]; g and out in the compute type, with row strides; one warp per (token, head).
+// gate: 0 none, 1 silu (g / (1 + exp(-g))), 2 sigmoid.  w may be null (no norm: out = o * gate * scale).
+// ---------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float gate_value(float g, int kind) {
+  if (kind == 1) return g / (1.f + expf(-g));
+  if (kind == 2) return 1.f / (1.f + expf(-g));
+  return 1.f;
+}
+
+template <typename T, typename TI>
+__global__ void head_norm_gate_kernel(const TI* __restrict__ o, long ldo, const T* __restrict__ g, long ldg,
+                                      const float* __restrict__ w, float eps, T* __restrict__ out, long ldout, float scale,
+                                      int gate, long items, int H, int D) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long item = (long)blockIdx.x * warps + warp;
+  if (item >= items) return;
+  const long t = item / H;
+  const int h = (int)(item - t * H);
+  const TI* x = o + (size_t)t * ldo + (size_t)h * D;
+  float rstd = 1.f;
+  if (w) {
+    float ss = 0.f;
+    for (int d = lane; d < D; d += 32) { const float val = to_f32(x[d]); ss = fmaf(val, val, ss); }
+    ss = warp_sum(ss);
+    rstd = rsqrtf(ss / (float)D + eps);
+  }
+  const T* gr = g ? g + (size_t)t * ldg + (size_t)h * D : nullptr;
+  T* dst = out + (size_t)t * ldout + (size_t)h * D;
+  for (int d = lane; d < D; d += 32) {
+    float val = to_f32(x[d]) * rstd;
+    if (w) val *= w[d];
+    if (gr) val *= gate_value(to_f32(gr[d]), gate);
+    dst[d] = from_f32<T>(val * scale);
+  }
+}
+
+extern "C" int qe_head_norm_gate(const void* o, long ldo, int o_f32, const void* g, long ldg, const float* w, float eps,
+                                 void* out, long ldout, float scale, int gate, int T, int H, int D, int dtype,
+                                 cudaStream_t stream) {
+  if (T <= 0) return 0;
+  const long items = (long)T * H;
+  const int warps = 8;
+  const unsigned blocks = (unsigned)((items + warps - 1) / warps);
+#define HNG(TT, TI) qe_launch(head_norm_gate_kernel<TT, TI>, dim3(blocks), dim3(warps * 32), 0, stream, (const TI*)o, ldo, \
+                              (const TT*)g, ldg, w, eps, (TT*)out, ldout, scale, gate, items, H, D)
+  if (dtype == QE_DTYPE_F32) HNG(float, float);
+  else if (dtype == QE_DTYPE_BF16) { if (o_f32) HNG(__nv_bfloat16, float); else HNG(__nv_bfloat16, __nv_bfloat16); }
+  else QE_REFUSE("head_norm_gate: unknown dtype %d", dtype);
+#undef HNG
+  QE_CHECK_LAUNCH("head_norm_gate");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// acc = (first ? 0 : acc) + scale * x, in float32: the weighted sum of mixers that run side by side and
+// cannot share one output product.
+// ---------------------------------------------------------------------------------------------------------
+template <typename TA, typename TX>
+__global__ void scaled_add_kernel(TA* __restrict__ acc, const TX* __restrict__ x, float scale, int first, long n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long e = (long)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (long)gridDim.x * blockDim.x)
+    acc[e] = from_f32<TA>((first ? 0.f : to_f32(acc[e])) + scale * to_f32(x[e]));
+}
+
+extern "C" int qe_scaled_add(void* acc, int acc_dtype, const void* x, int x_dtype, float scale, int first, long n,
+                             cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const unsigned blocks = (unsigned)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+#define SADD(TA, TX) qe_launch(scaled_add_kernel<TA, TX>, dim3(blocks), dim3(256), 0, stream, (TA*)acc, (const TX*)x, scale, first, n)
+  if (acc_dtype == QE_DTYPE_F32 && x_dtype == QE_DTYPE_F32) SADD(float, float);
+  else if (acc_dtype == QE_DTYPE_F32 && x_dtype == QE_DTYPE_BF16) SADD(float, __nv_bfloat16);
+  else if (acc_dtype == QE_DTYPE_BF16 && x_dtype == QE_DTYPE_F32) SADD(__nv_bfloat16, float);
+  else if (acc_dtype == QE_DTYPE_BF16 && x_dtype == QE_DTYPE_BF16) SADD(__nv_bfloat16, __nv_bfloat16);
+  else QE_REFUSE("scaled_add: unknown dtypes %d, %d", acc_dtype, x_dtype);
+#undef SADD
+  QE_CHECK_LAUNCH("scaled_add");
+  return 0;
+}

@@ -4,7 +4,10 @@ Which layers exist, what each is made of, and in which order they run is data
 (``ModelLayout``), written by an architecture's layout function from its
 configuration.  The plan is a list of entries; an entry names the layer to run,
 the cache slot it uses, and whether it writes that slot (a layer may run twice
-under two slots, or read the slot another layer wrote).
+under two slots, or read the slot another layer wrote).  A mixer made of
+several mixers names one slot for each (a tuple); an entry may also ask for
+the embedding output to be added to the stream before it runs (a pass over the
+same layers that starts again from the tokens).
 
 The reference's model runs embedding, its layers in order, the final norm and
 the head over every row (src/models/qwen3/model.py:347-360, 420-422); here the
@@ -37,8 +40,16 @@ class LayerSpec:
 @dataclass(frozen=True)
 class PlanEntry:
     layer: int                  # index into ModelLayout.layers
-    cache_slot: Optional[int]   # which cache slot this run uses (None: the mixer keeps nothing)
+    cache_slot: object          # which cache slot this run uses (None: the mixer keeps nothing; a tuple: one per
+                                # cache description of a mixer that has several, in the order of its cache_specs())
     write_cache: bool = True    # False: read what another entry wrote into the slot
+    add_embedding: bool = False  # the embedding output (token rows x the model's scale) is added to the stream first
+
+    @property
+    def slots(self) -> tuple:
+        if self.cache_slot is None:
+            return ()
+        return tuple(self.cache_slot) if isinstance(self.cache_slot, (tuple, list)) else (self.cache_slot,)
 
 
 @dataclass(frozen=True)
@@ -50,9 +61,10 @@ class ModelLayout:
     final_norm: PartSpec
     embed_name: str = "model.embed_tokens.weight"
     final_norm_prefix: str = "model.norm."
-    head_name: str = "lm_head.weight"
+    head_name: Optional[str] = "lm_head.weight"      # None: the model has no head tensor (the embedding table serves)
     tie_head: bool = True
     max_positions: Optional[int] = None
+    embed_scale: float = 1.0    # the embedding output is the table's row times this (the head uses the table as it is)
 
 
 class DecoderModel:
@@ -64,30 +76,31 @@ class DecoderModel:
         self.head: Optional[torch.Tensor] = None
         self.dtype: Optional[torch.dtype] = None
         self.device = None
-        n_slots = 1 + max((e.cache_slot for e in layout.plan if e.cache_slot is not None), default=-1)
+        n_slots = 1 + max((s for e in layout.plan for s in e.slots), default=-1)
         specs: list[Optional[CacheSpec]] = [None] * n_slots
         writers = [0] * n_slots
         for e in layout.plan:
             if not (0 <= e.layer < len(self.blocks)):
                 raise ValueError(f"plan names layer {e.layer}, the model has {len(self.blocks)}")
-            if e.cache_slot is None:
+            if not e.slots:
                 continue
-            spec = self.blocks[e.layer].mixer.cache_spec()
-            if spec is None:
-                raise ValueError(f"plan gives layer {e.layer} a cache slot but its mixer keeps nothing")
-            if specs[e.cache_slot] is not None and specs[e.cache_slot] != spec:
-                raise ValueError(f"cache slot {e.cache_slot} is used by layers with different needs")
-            specs[e.cache_slot] = spec
-            writers[e.cache_slot] += int(e.write_cache)
+            needs = self.blocks[e.layer].mixer.cache_specs()
+            if len(needs) != len(e.slots):
+                raise ValueError(f"plan gives layer {e.layer} {len(e.slots)} cache slot(s) but its mixer keeps {len(needs)} cache(s)")
+            for slot, spec in zip(e.slots, needs):
+                if specs[slot] is not None and specs[slot] != spec:
+                    raise ValueError(f"cache slot {slot} is used by layers with different needs")
+                specs[slot] = spec
+                writers[slot] += int(e.write_cache)
         for slot, n in enumerate(writers):
             if specs[slot] is not None and n != 1:
                 raise ValueError(f"cache slot {slot} must be written by exactly one plan entry, not {n}")
         self._cache_specs = specs
         geos = []
         for b in self.blocks:
-            geo = b.mixer.attention_geometry()
-            if geo is not None and geo not in geos:
-                geos.append(geo)
+            for geo in b.mixer.attention_geometries():
+                if geo not in geos:
+                    geos.append(geo)
         self.attention_geometries = tuple(geos)
         self.capturable = all(getattr(b, "capturable", True) and getattr(b.mixer, "capturable", True) for b in self.blocks)
 
@@ -101,8 +114,11 @@ class DecoderModel:
         for ls, block in zip(lo.layers, self.blocks):
             specs += block.weight_specs(ls.weight_prefix)
         specs += self.final_norm.weight_specs(lo.final_norm_prefix)
-        specs.append(WeightSpec(lo.head_name, (lo.vocab_size, lo.hidden_size), MATRIX,
-                                optional=lo.tie_head))
+        if lo.head_name is not None:
+            specs.append(WeightSpec(lo.head_name, (lo.vocab_size, lo.hidden_size), MATRIX,
+                                    optional=lo.tie_head))
+        elif not lo.tie_head:
+            raise ValueError("a model without a head tensor must tie its head to the embedding")
         return specs
 
     def load_weights(self, source: TensorSource, dtype: torch.dtype, device, where: str = "checkpoint") -> None:
@@ -115,7 +131,7 @@ class DecoderModel:
         self.final_norm.load(lo.final_norm_prefix, source, dtype, device)
         if lo.tie_head:
             self.head = self.embed            # the same storage (model.py:417-418)
-            if lo.head_name in set(source.names()):
+            if lo.head_name is not None and lo.head_name in set(source.names()):
                 # the reference lets such a tensor overwrite the shared storage (whichever of the two is read
                 # last wins); here the embedding is the one that counts, and the user is told
                 import warnings
@@ -154,14 +170,24 @@ class DecoderModel:
         lo = self.layout
         T, H = ctx.num_tokens, lo.hidden_size
         stream = ops.ResidualStream.for_step(ctx.arena.alloc, T, H, ctx.dtype)
-        ops.embedding(ctx.token_ids, self.embed, stream)
-        views = [(cache.layer_view(e.cache_slot), cache.group_of_slot[e.cache_slot][0]) if e.cache_slot is not None
-                 else (None, None) for e in lo.plan]
+        ops.embedding(ctx.token_ids, self.embed, stream, scale=lo.embed_scale)
+        views = []
+        for e in lo.plan:
+            if not e.slots:
+                views.append((None, None))
+            elif isinstance(e.cache_slot, (tuple, list)):
+                views.append((tuple(cache.layer_view(s) for s in e.slots), tuple(cache.group_of_slot[s][0] for s in e.slots)))
+            else:
+                views.append((cache.layer_view(e.cache_slot), cache.group_of_slot[e.cache_slot][0]))
         for i, entry in enumerate(lo.plan):
             view, group = views[i]
             # a hint for mixers that can ask for it ahead of time: the cache that the next entry of the plan
             # with a cache of the same group will read (the same pages at the same places)
-            ctx.extras["next_cache"] = next((v for v, g in views[i + 1:] if v is not None and g == group and v is not view), None)
+            ctx.extras["next_cache"] = None if isinstance(view, tuple) else next(
+                (v for v, g in views[i + 1:] if v is not None and not isinstance(v, tuple) and g == group and v is not view), None)
+            if entry.add_embedding:
+                # a pass that starts again from the tokens: the rows of the table, scaled, are added to the stream
+                ops.embedding(ctx.token_ids, self.embed, stream, scale=lo.embed_scale, accumulate=True)
             # and the weights that the step reads first after this block
             nxt = lo.plan[i + 1].layer if i + 1 < len(lo.plan) else None
             ctx.extras["weights_after_ffn"] = self.blocks[nxt].first_weights() if nxt is not None else None

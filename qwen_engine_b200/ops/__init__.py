@@ -150,13 +150,19 @@ def prepare_matrix(w: torch.Tensor) -> torch.Tensor:
 
 
 def embedding(token_ids: torch.Tensor, table: torch.Tensor, out,
-              ssq: Optional[torch.Tensor] = None) -> None:
-    """out[t] = float32(table[token_ids[t]]); out is the float32 residual stream [T, H].  With ``ssq``
+              ssq: Optional[torch.Tensor] = None, scale: float = 1.0, accumulate: bool = False) -> None:
+    """out[t] = float32(table[token_ids[t]]) * scale; out is the float32 residual stream [T, H].  With ``ssq``
     [T, P] float32, ssq[t, 0] gets the row's sum of squares (one partial sum per row).  ``out`` may be a
-    ``ResidualStream``: its rows are written and, if it keeps sums of squares, those too."""
+    ``ResidualStream``: its rows are written and, if it keeps sums of squares, those too.
+    ``accumulate``: the scaled rows are added to what the stream holds (its pending branch output stays
+    pending; sums of squares are no longer known)."""
     if isinstance(out, ResidualStream):
         stream = out
-        embedding(token_ids, table, stream.resid, stream.ssq)
+        if accumulate:
+            embedding(token_ids, table, stream.resid, None, scale, True)
+            stream.n_ssq = 0
+            return
+        embedding(token_ids, table, stream.resid, stream.ssq, scale)
         stream.has_delta, stream.n_ssq = False, (1 if stream.ssq is not None else 0)
         return
     _i32(token_ids, "token_ids")
@@ -167,7 +173,8 @@ def embedding(token_ids: torch.Tensor, table: torch.Tensor, out,
         _need(ssq.dtype == torch.float32 and ssq.dim() == 2 and ssq.shape[0] == T and ssq.is_contiguous(),
               "embedding: ssq must be float32 [T, P]")
     _check(lib().qe_embedding(_ptr(token_ids), _ptr(table), _ptr(out), T, H, V, _dt(table), _ptr(ssq),
-                              int(ssq.shape[1]) if ssq is not None else 0, _stream()), "embedding")
+                              int(ssq.shape[1]) if ssq is not None else 0, ctypes.c_float(scale), int(bool(accumulate)),
+                              _stream()), "embedding")
 
 
 def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
@@ -771,15 +778,17 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, q_norm_w: 
                           k_norm_w: Optional[torch.Tensor], eps: float, inv_freq: Optional[torch.Tensor],
                           rotary_dim: int, kv_pages: Optional[torch.Tensor], slot_mapping: Optional[torch.Tensor],
                           num_heads: int, num_kv_heads: int, head_dim: int, write_kv: bool = True,
-                          cos_sin: Optional[torch.Tensor] = None) -> None:
-    """On the stacked projection output qkv [T, (Hq + 2 Hkv) D], in place: per-head RMS norm of q and
-    k (if weights are given), half-split rotation by positions (if inv_freq is given); then k and v
-    are written to the slots of ``slot_mapping`` in ``kv_pages`` [pages, 2, Hkv, page, D]."""
+                          cos_sin: Optional[torch.Tensor] = None, norm_dim: Optional[int] = None) -> None:
+    """On the stacked projection output qkv [T, (Hq + 2 Hkv) D] (rows may be strided: the leading columns
+    of a wider product), in place: per-head RMS norm of q and k (if weights are given), half-split rotation
+    by positions (if inv_freq is given); then k and v are written to the slots of ``slot_mapping`` in
+    ``kv_pages`` [pages, 2, Hkv, page, D].  ``norm_dim``: the channels the norm's mean runs over, where a
+    head is padded with zero channels up to D."""
     T = qkv.shape[0]
     Hq, Hkv, D = num_heads, num_kv_heads, head_dim
-    _need(qkv.shape == (T, (Hq + 2 * Hkv) * D) and qkv.is_contiguous(), "qk_norm_rope_kv_write: qkv must be [T, (Hq+2Hkv)D]")
+    _need(qkv.shape == (T, (Hq + 2 * Hkv) * D) and qkv.stride(1) == 1, "qk_norm_rope_kv_write: qkv must be [T, (Hq+2Hkv)D]")
     _i32(positions, "positions")
-    stride = qkv.shape[1]
+    stride = qkv.stride(0)
     q = qkv
     k = qkv[:, Hq * D:]
     v = qkv[:, (Hq + Hkv) * D:]
@@ -803,7 +812,7 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, q_norm_w: 
         _ptr(q_norm_w), _ptr(k_norm_w), ctypes.c_float(eps), _ptr(inv_freq),
         _ptr(cos_sin if (cos_sin is not None and D == 128 and rotary_dim == D) else None), int(rotary_dim),
         _ptr(kv_pages if write_kv else None), _ptr(slot_mapping if write_kv else None),
-        T, Hq, Hkv, D, page_size, int(bool(write_kv)), _dt(qkv), _stream()), "qk_norm_rope_kv_write")
+        T, Hq, Hkv, D, page_size, int(bool(write_kv)), _dt(qkv), int(norm_dim or D), _stream()), "qk_norm_rope_kv_write")
 
 
 def rope_neox(q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor,
@@ -818,7 +827,7 @@ def rope_neox(q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor, inv_fre
         ctypes.c_void_p(q.data_ptr()), ctypes.c_void_p(k.data_ptr()), ctypes.c_void_p(0),
         ctypes.c_long(q.stride(0)), ctypes.c_long(k.stride(0)), ctypes.c_long(0), _ptr(positions),
         _ptr(None), _ptr(None), ctypes.c_float(0.0), _ptr(inv_freq), _ptr(None), int(rotary_dim),
-        _ptr(None), _ptr(None), T, Hq, Hkv, D, 1, 0, _dt(q), _stream()), "rope_neox")
+        _ptr(None), _ptr(None), T, Hq, Hkv, D, 1, 0, _dt(q), D, _stream()), "rope_neox")
 
 
 def flash_supported(dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_dim: int) -> bool:
@@ -876,13 +885,20 @@ def _plan_tc_tiles(tiles: list, Hkv: int) -> tuple[list[int], int, list[int], in
     return [x for _, item in out for x in item], n_parts, list(sched), n_ctas
 
 
+def split_geometry(geo) -> tuple:
+    """(heads, kv heads, head size, window, biased) of a geometry; the fifth entry (scores biased by distance:
+    only some kernels take them) may be left out."""
+    Hq, Hkv, D, window = geo[:4]
+    return Hq, Hkv, D, window, bool(len(geo) > 4 and geo[4])
+
+
 def plan_attention(q_lens: list[int], ctx_lens: list[int], page_size: int,
                    geometries=(), dtype: torch.dtype = torch.float32,
                    uniform_splits: Optional[dict] = None) -> dict[str, list[int]]:
     """Work lists of the attention kernels for one step's batch, as named int32 lists that the
     step function copies to the device with the rest of the step's metadata.
 
-    ``geometries``: the (heads, kv heads, head size, window) of the model's attention layers.
+    ``geometries``: the (heads, kv heads, head size, window[, biased by distance]) of the model's attention layers.
     ``tiles`` serves the generic kernel; for each geometry the flash kernel takes, ``fa<i>_items``
     and ``fa<i>_merge`` hold its work and merge items and ``fa<i>_info`` = [parts, rows per part,
     whether every item has at most 16 rows, the most rows of an item, the number of parts of every
@@ -897,12 +913,12 @@ def plan_attention(q_lens: list[int], ctx_lens: list[int], page_size: int,
             tiles += [r, q0]
     plan = {"tiles": tiles}
     for gi, geo in enumerate(geometries):
-        Hq, Hkv, D, window = geo
+        Hq, Hkv, D, window, biased = split_geometry(geo)
         if not flash_supported(dtype, Hq, Hkv, D):
             continue
         G = Hq // Hkv
         tpt = FLASH_ROWS // G
-        use_tc = uniform_splits is None and tc_attention_supported(dtype, Hq, Hkv, D, page_size)
+        use_tc = uniform_splits is None and not biased and tc_attention_supported(dtype, Hq, Hkv, D, page_size)
         on_tc = [use_tc and n * G >= TC_MIN_ROWS for n in q_lens]
         tc_tiles: list = []
         base = sum(-(-n // tpt) for n, tc in zip(q_lens, on_tc) if not tc) * Hkv
@@ -962,7 +978,7 @@ def decode_splits(num_reqs: int, max_tokens: int, geometries, dtype: torch.dtype
     tables hold up to ``max_tokens`` tokens: enough parts to fill the GPU, none shorter than a split."""
     out = {}
     for geo in geometries:
-        Hq, Hkv, D, window = geo
+        Hq, Hkv, D, window, _ = split_geometry(geo)
         span = min(max_tokens, window) if window else max_tokens
         target = FLASH_TARGET_CTAS
         if (DECODE_ATTENTION_MMA and DECODE_ATTENTION_MMA_WIDE and dtype == torch.bfloat16 and D == 128
@@ -1019,10 +1035,13 @@ def _decode_mma_serves(plan, key, qkv: torch.Tensor, Hq: int, Hkv: int, D: int) 
 
 def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: torch.Tensor, ctx,
                     out: torch.Tensor, scale: float, window: int, num_heads: int, num_kv_heads: int,
-                    head_dim: int, next_pages: Optional[torch.Tensor] = None) -> None:
+                    head_dim: int, next_pages: Optional[torch.Tensor] = None,
+                    slopes: Optional[torch.Tensor] = None) -> None:
     """Attention of the step's queries (the q part of qkv [T, (Hq+2Hkv) D]) over the keys and values
     of their requests in ``kv_pages``; out [T, Hq D].  ``ctx`` is the StepContext (cu_q, ctx_lens,
     the plan that ``plan_attention`` made, and the arena for the parts of split contexts).
+
+    ``slopes`` (float32 [Hq]): the score of query i and key j of head h is scale q.k - slopes[h] (i - j).
 
     ``next_pages``: the cache of the layer that runs after this one, if it has the same shape (the same
     pages at the same places): a decode step's kernel may ask L2 for that layer's keys and values."""
@@ -1034,8 +1053,12 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
     _i32(block_tables, "block_tables")
     global last_attention_kernel
     plan = ctx.attn_plan
-    key = plan.get("geometry_index", {}).get((Hq, Hkv, D, window))
+    if slopes is not None:
+        _need(slopes.dtype == torch.float32 and slopes.numel() == Hq and slopes.is_contiguous(), "paged_attention: slopes must be float32 [Hq]")
+    index = plan.get("geometry_index", {})
+    key = index.get((Hq, Hkv, D, window, True)) if slopes is not None else index.get((Hq, Hkv, D, window), index.get((Hq, Hkv, D, window, False)))
     if key is not None and f"tc{key}_items" in plan:
+        _need(slopes is None, "paged_attention: the tcgen05 kernel takes no distance bias")
         last_attention_kernel = "flash_attention_tc"
         tc_items = plan[f"tc{key}_items"]
         tc_parts, tc_rows, tc_ctas = plan[f"tc{key}_info_host"]
@@ -1064,7 +1087,7 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
         counters = _merge_counters(qkv.device) if 0 < n_parts * Hkv <= _MERGE_COUNTERS else None
         # every request in the same few parts: the parts of a request form a cluster and meet on chip
         cluster = int(same_parts) if DECODE_ATTENTION_CLUSTERS and n_items == n_parts else 0
-        if _decode_mma_serves(plan, key, qkv, Hq, Hkv, D):
+        if slopes is None and _decode_mma_serves(plan, key, qkv, Hq, Hkv, D):
             # decoded tokens: every warp streams key groups of its own through the tensor cores
             last_attention_kernel = "decode_attention_mma"
             lib().qe_decode_attention_mma_stages(int(DECODE_ATTENTION_MMA_STAGES))
@@ -1087,7 +1110,7 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
             _ptr(qkv), ctypes.c_long(qkv.stride(0)), _ptr(kv_pages), _ptr(block_tables), int(block_tables.shape[1]),
             _ptr(ctx.cu_q), _ptr(ctx.ctx_lens), _ptr(items), n_items, _ptr(merge), n_merge, _ptr(out),
             _ptr(part_acc), _ptr(part_ml), int(part_rows), _ptr(counters), int(small_tiles), ctypes.c_float(scale), int(window),
-            Hq, Hkv, D, int(kv_pages.shape[3]), _stream()), "flash_attention")
+            Hq, Hkv, D, int(kv_pages.shape[3]), _ptr(slopes), _stream()), "flash_attention")
         return
     tiles = plan["tiles"]
     n_tiles = tiles.numel() // 2
@@ -1095,7 +1118,7 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
     _check(lib().qe_paged_attention_generic(
         _ptr(qkv), ctypes.c_long(qkv.stride(0)), _ptr(kv_pages), _ptr(block_tables), int(block_tables.shape[1]),
         _ptr(ctx.cu_q), _ptr(ctx.ctx_lens), _ptr(tiles), n_tiles, _ptr(out), ctypes.c_float(scale), int(window),
-        Hq, Hkv, D, int(kv_pages.shape[3]), _dt(qkv), _stream()), "paged_attention")
+        Hq, Hkv, D, int(kv_pages.shape[3]), _dt(qkv), _ptr(slopes), _stream()), "paged_attention")
 
 
 def place_tokens(token_ids: torch.Tensor, rows: torch.Tensor, src: torch.Tensor, src_index: torch.Tensor) -> None:
@@ -1125,6 +1148,97 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
     _need(I2 % 2 == 0 and out.shape == (T, I2 // 2) and out.dtype == gate_up.dtype
           and out.is_contiguous() and gate_up.is_contiguous(), "silu_mul: out must be [T, I] for gate_up [T, 2I]")
     _check(lib().qe_silu_mul(_ptr(gate_up), _ptr(out), T, I2 // 2, _dt(out), _stream()), "silu_mul")
+
+
+GATE_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def act_mul(gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> None:
+    """out[t, i] = act(gate_up[t, i]) * gate_up[t, I + i]; act "silu", or "gelu_tanh":
+    0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).  Float32 arithmetic, rounded once."""
+    T, I2 = gate_up.shape
+    _need(activation in GATE_ACTIVATIONS, f"act_mul: unknown activation {activation!r}")
+    _need(I2 % 2 == 0 and out.shape == (T, I2 // 2) and out.dtype == gate_up.dtype
+          and out.is_contiguous() and gate_up.is_contiguous(), "act_mul: out must be [T, I] for gate_up [T, 2I]")
+    _check(lib().qe_act_mul(_ptr(gate_up), _ptr(out), T, I2 // 2, _dt(out), GATE_ACTIVATIONS[activation], _stream()), "act_mul")
+
+
+def _rows(t: torch.Tensor, name: str) -> None:
+    _need(t.dim() == 2 and t.stride(1) == 1, f"{name} must be rows with unit stride along the columns")
+
+
+def channel_decay(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], tau: float, out: torch.Tensor) -> None:
+    """out[t, n] = sigmoid(z)^(1 / tau) with z = a[t] . w[n] + bias[n], in float32: the decay of a recurrence
+    from the second half of a low-rank pair.  a [T, R] (rows may be strided), w [N, R], out float32 [T, N]."""
+    _rows(a, "channel_decay: a")
+    T, R = a.shape
+    N = w.shape[0]
+    _need(w.shape == (N, R) and w.dtype == a.dtype and w.is_contiguous(), "channel_decay: w must be [N, R] in a's dtype")
+    _need(out.shape == (T, N) and out.dtype == torch.float32 and out.is_contiguous(), "channel_decay: out must be float32 [T, N]")
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.shape == (N,) and bias.is_contiguous(), "channel_decay: bias must be float32 [N]")
+    _check(lib().qe_channel_decay(_ptr(a), ctypes.c_long(a.stride(0)), _ptr(w), _ptr(bias), ctypes.c_float(tau), _ptr(out),
+                                  T, N, R, _dt(a), _stream()), "channel_decay")
+
+
+def linear_attention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, alpha: torch.Tensor, state: torch.Tensor,
+                          ctx, out: torch.Tensor, q_scale: float, num_heads: int, key_dim: int, value_dim: int,
+                          write_state: bool = True) -> None:
+    """The recurrence S <- diag(alpha_t) S + k_t v_t^T, o_t = S^T (q_scale q_t) per head, over the step's
+    tokens of every request, from the state its slot holds (zero for a request without context) to the
+    state after its last token.  q, k [T, H dk] and v [T, H dv] in the compute type (rows may be strided),
+    alpha float32 [T, H dk], state float32 [slots, H, dv, dk], out float32 [T, H dv]."""
+    H, dk, dv = num_heads, key_dim, value_dim
+    T = q.shape[0]
+    for t, name, width in ((q, "q", H * dk), (k, "k", H * dk), (v, "v", H * dv)):
+        _rows(t, f"linear_attention_scan: {name}")
+        _need(t.shape == (T, width) and t.dtype == q.dtype, f"linear_attention_scan: {name} must be [T, {width}]")
+    _need(alpha.shape == (T, H * dk) and alpha.dtype == torch.float32 and alpha.is_contiguous(),
+          "linear_attention_scan: alpha must be float32 [T, H dk]")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (H, dv, dk),
+          "linear_attention_scan: state must be float32 [slots, H, dv, dk]")
+    _need(out.shape == (T, H * dv) and out.dtype == torch.float32 and out.is_contiguous(),
+          "linear_attention_scan: out must be float32 [T, H dv]")
+    _check(lib().qe_linear_attention_scan(
+        _ptr(q), _ptr(k), _ptr(v), ctypes.c_long(q.stride(0)), ctypes.c_long(k.stride(0)), ctypes.c_long(v.stride(0)),
+        _ptr(alpha), _ptr(state), _ptr(ctx.cu_q), _ptr(ctx.ctx_lens), _ptr(ctx.slot_ids), _ptr(out), ctypes.c_float(q_scale),
+        int(ctx.num_reqs), int(ctx.max_q_len), H, dk, dv, int(bool(write_state)), _dt(q), _stream()), "linear_attention_scan")
+
+
+_GATES = {None: 0, "silu": 1, "sigmoid": 2}
+
+
+def head_norm_gate(x: torch.Tensor, gate: Optional[torch.Tensor], weight: Optional[torch.Tensor], eps: float,
+                   out: torch.Tensor, num_heads: int, head_dim: int, gate_kind: Optional[str] = "silu",
+                   scale: float = 1.0) -> None:
+    """out[t, h] = x[t, h] / rms(x[t, h]) * weight * g(gate[t, h]) * scale for every head of every token:
+    the RMS norm over a head's channels (left out when ``weight`` is None) and an output gate (silu or
+    sigmoid of ``gate``; left out when ``gate`` is None), float32 arithmetic, rounded once.
+    x [T, H D] float32 or the compute type; gate and out in the compute type; rows of all three may be strided."""
+    T = x.shape[0]
+    H, D = num_heads, head_dim
+    _need(gate_kind in _GATES, f"head_norm_gate: unknown gate {gate_kind!r}")
+    for t, name in ((x, "x"), (out, "out")) + (((gate, "gate"),) if gate is not None else ()):
+        _rows(t, f"head_norm_gate: {name}")
+        _need(t.shape == (T, H * D), f"head_norm_gate: {name} must be [T, H D]")
+    _need(x.dtype in (torch.float32, out.dtype), "head_norm_gate: x must be float32 or out's dtype")
+    if gate is not None:
+        _need(gate.dtype == out.dtype, "head_norm_gate: gate must have out's dtype")
+    if weight is not None:
+        _need(weight.dtype == torch.float32 and weight.shape == (D,) and weight.is_contiguous(), "head_norm_gate: weight must be float32 [D]")
+    _check(lib().qe_head_norm_gate(
+        _ptr(x), ctypes.c_long(x.stride(0)), int(x.dtype == torch.float32), _ptr(gate),
+        ctypes.c_long(gate.stride(0) if gate is not None else 0), _ptr(weight), ctypes.c_float(eps), _ptr(out),
+        ctypes.c_long(out.stride(0)), ctypes.c_float(scale), _GATES[gate_kind if gate is not None else None], T, H, D, _dt(out),
+        _stream()), "head_norm_gate")
+
+
+def scaled_add(acc: torch.Tensor, x: torch.Tensor, scale: float, first: bool = False) -> None:
+    """acc = (0 if first else acc) + scale * x, element by element in float32; acc and x of one shape, each float32
+    or the compute type."""
+    _need(acc.shape == x.shape and acc.is_contiguous() and x.is_contiguous(), "scaled_add: two contiguous tensors of one shape")
+    _check(lib().qe_scaled_add(_ptr(acc), _dt(acc), _ptr(x), _dt(x), ctypes.c_float(scale), int(bool(first)),
+                               ctypes.c_long(acc.numel()), _stream()), "scaled_add")
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:

@@ -4,10 +4,12 @@ from .base import (Arena, Block, FeedForward, GroupStepView, Mixer, Norm, Part, 
 from .norm import RMSNorm
 from .rope import NeoxRope
 from .attention import GQAAttention
+from .linear_attention import GatedLinearAttention
+from .parallel import ParallelMixers
 from .mlp import SwiGLU
 from .block import PreNormBlock
 
 __all__ = ["Arena", "Block", "FeedForward", "GroupStepView", "Mixer", "Norm", "Part", "PartSpec",
            "PositionEncoding", "StepContext", "register", "NORMS", "POSITION_ENCODINGS", "MIXERS",
-           "FEED_FORWARDS", "BLOCKS", "RMSNorm", "NeoxRope", "GQAAttention", "SwiGLU",
+           "FEED_FORWARDS", "BLOCKS", "RMSNorm", "NeoxRope", "GQAAttention", "GatedLinearAttention", "ParallelMixers", "SwiGLU",
            "PreNormBlock"]

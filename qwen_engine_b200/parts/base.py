@@ -245,10 +245,37 @@ class Mixer(Part):
     def cache_spec(self) -> Optional[CacheSpec]:
         return None
 
+    def cache_specs(self) -> list:
+        """Every cache the mixer keeps: one description for most mixers, several for a mixer made of
+        mixers.  ``forward`` then gets a tuple of caches and of groups in this order."""
+        spec = self.cache_spec()
+        return [] if spec is None else [spec]
+
     def attention_geometry(self) -> Optional[tuple[int, int, int, int]]:
         """(heads, kv heads, head size, window or 0) if the mixer calls ``ops.paged_attention``:
         the step function plans the attention kernels' work once per step for every geometry."""
         return None
+
+    def attention_geometries(self) -> list:
+        geo = self.attention_geometry()
+        return [] if geo is None else [geo]
+
+    # A mixer that ends in an output projection may also offer its two halves apart, so that a mixer made
+    # of several can run their output projections as ONE product over the joined inner rows:
+    #   inner_width            columns of what goes into the output projection (None: not offered)
+    #   output_weight()        the [hidden, inner_width] matrix, loaded
+    #   mix_into(ctx, x, cache, group, inner, write_cache, scale)
+    #                          everything before the output projection; ``inner`` [T, inner_width] may be a
+    #                          column slice of a wider buffer (unit stride along columns); what is written
+    #                          is multiplied by ``scale`` in float32 before it is rounded
+    inner_width: Optional[int] = None
+
+    def output_weight(self) -> torch.Tensor:
+        raise NotImplementedError
+
+    def mix_into(self, ctx: "StepContext", x: torch.Tensor, cache, group, inner: torch.Tensor,
+                 write_cache: bool = True, scale: float = 1.0) -> None:
+        raise NotImplementedError
 
     def forward(self, ctx: StepContext, x: torch.Tensor, cache: Optional[torch.Tensor],
                 group: Optional[int], out: torch.Tensor, write_cache: bool = True) -> None:

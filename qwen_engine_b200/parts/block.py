@@ -1,26 +1,30 @@
 """The pre-norm residual block: x += mixer(norm1(x)); x += ffn(norm2(x))
 (reference src/models/qwen3/model.py:278-298).  Each add is carried to the
-next norm as a pending delta so that one kernel adds and norms."""
+next norm as a pending delta so that one kernel adds and norms.  A layer may
+have no feed-forward (``feed_forward`` None): it is then the first sublayer alone."""
 from __future__ import annotations
 
 from .. import ops
+from typing import Optional
+
 from .base import Block, PartSpec, StepContext, register
 
 
 @register("block", "pre_norm")
 class PreNormBlock(Block):
-    def __init__(self, hidden_size: int, mixer: PartSpec, feed_forward: PartSpec, norm: PartSpec,
+    def __init__(self, hidden_size: int, mixer: PartSpec, feed_forward: Optional[PartSpec], norm: PartSpec,
                  mixer_prefix: str = "self_attn.", ffn_prefix: str = "mlp.",
                  norm1_prefix: str = "input_layernorm.", norm2_prefix: str = "post_attention_layernorm."):
         self.hidden_size = hidden_size
         self.norm1 = norm.build("norm")
-        self.norm2 = norm.build("norm")
+        self.norm2 = norm.build("norm") if feed_forward is not None else None
         self.mixer = mixer.build("mixer")
-        self.ffn = feed_forward.build("feed_forward")
+        self.ffn = feed_forward.build("feed_forward") if feed_forward is not None else None
         self.prefixes = (norm1_prefix, mixer_prefix, norm2_prefix, ffn_prefix)
 
     def _parts(self):
-        return zip((self.norm1, self.mixer, self.norm2, self.ffn), self.prefixes)
+        return [(part, p) for part, p in zip((self.norm1, self.mixer, self.norm2, self.ffn), self.prefixes)
+                if part is not None]
 
     @property
     def capturable(self) -> bool:
@@ -41,9 +45,12 @@ class PreNormBlock(Block):
         h = self.norm1.normed(ctx, stream, lazy=self.mixer.takes_lazy_input)
         out = self._branch_out(stream, self.mixer)
         if getattr(ctx, "extras", None) is not None:
-            ctx.extras["weights_after_mixer"] = self.ffn.first_weights()
+            ctx.extras["weights_after_mixer"] = self.ffn.first_weights() if self.ffn is not None else None
         self.mixer.forward(ctx, h, cache, group, out, write_cache)
         self._branch_done(stream, out)
+        if self.ffn is None:
+            ctx.arena.release(mark)
+            return
         h = self.norm2.normed(ctx, stream, lazy=self.ffn.takes_lazy_input)
         out = self._branch_out(stream, self.ffn)
         self.ffn.forward(ctx, h, out)

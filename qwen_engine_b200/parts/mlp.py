@@ -1,7 +1,13 @@
 """SwiGLU feed-forward: down(silu(gate(x)) * up(x)), no biases
 (reference src/models/qwen3/model.py:227-237; silu(g) = g / (1 + exp(-g)) in
 float32, src/layers/fused_ops/silumul.py:50-53).  gate and up are one product
-over the stacked weights."""
+over the stacked weights.
+
+The same part serves other gated feed-forwards: ``activation`` names the
+function on the gate ("silu", or "gelu_tanh": 0.5 z (1 + tanh(sqrt(2/pi) (z +
+0.044715 z^3)))), ``names`` the three tensors.  The products that form SiLU-mul
+in their own epilogue are asked for "silu" only; another activation runs as
+product, activation kernel, product."""
 from __future__ import annotations
 
 import torch
@@ -15,28 +21,44 @@ from .base import FeedForward, StepContext, register, step_hint
 class SwiGLU(FeedForward):
     takes_lazy_input = True       # x goes to one product only
     writes_through_linear = True  # out is the out of the last product
-    def __init__(self, hidden_size: int, intermediate_size: int):
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu",
+                 names: tuple = ("gate_proj.weight", "up_proj.weight", "down_proj.weight")):
+        if activation not in ops.GATE_ACTIVATIONS:
+            raise ValueError(f"unknown activation {activation!r}; known: {sorted(ops.GATE_ACTIVATIONS)}")
         self.hidden_size = hidden_size
         self.intermediate_size = intermediate_size
+        self.activation = activation
+        self.names = tuple(names)
         self.w_gate_up = self.w_down = None
 
     def weight_specs(self, prefix: str) -> list[WeightSpec]:
         I, H = self.intermediate_size, self.hidden_size
-        return [WeightSpec(prefix + "gate_proj.weight", (I, H), MATRIX),
-                WeightSpec(prefix + "up_proj.weight", (I, H), MATRIX),
-                WeightSpec(prefix + "down_proj.weight", (H, I), MATRIX)]
+        gate, up, down = self.names
+        return [WeightSpec(prefix + gate, (I, H), MATRIX),
+                WeightSpec(prefix + up, (I, H), MATRIX),
+                WeightSpec(prefix + down, (H, I), MATRIX)]
 
     def load(self, prefix, source, dtype, device) -> None:
-        stacked = torch.cat([source.get(prefix + "gate_proj.weight"),
-                             source.get(prefix + "up_proj.weight")], dim=0)
+        gate, up, down = self.names
+        stacked = torch.cat([source.get(prefix + gate), source.get(prefix + up)], dim=0)
         self.w_gate_up = ops.prepare_matrix(stacked.to(dtype).to(device))
-        self.w_down = ops.prepare_matrix(source.get(prefix + "down_proj.weight").to(dtype).to(device))
+        self.w_down = ops.prepare_matrix(source.get(prefix + down).to(dtype).to(device))
 
     def first_weights(self):
         return self.w_gate_up
 
     def forward(self, ctx: StepContext, x, out) -> None:
         T, I = ctx.num_tokens, self.intermediate_size
+        if self.activation != "silu":
+            gate_up = ctx.arena.alloc((T, 2 * I), ctx.dtype)
+            act = ctx.arena.alloc((T, I), ctx.dtype)
+            ops.prefetch_next(self.w_down)
+            ops.linear(x, self.w_gate_up, gate_up)
+            ops.act_mul(gate_up, act, self.activation)
+            ops.prefetch_next(step_hint(ctx, "weights_after_ffn"))
+            ops.linear(act, self.w_down, out)
+            ops.prefetch_next(None)
+            return
         if ops.swiglu_fused_applies(T, I, self.hidden_size, ctx.dtype):
             # many rows: the activation comes out of the gate/up product's epilogue
             if isinstance(x, ops.NormedInput):

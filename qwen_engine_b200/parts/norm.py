@@ -5,6 +5,9 @@ y = x * rsqrt(mean(x^2) + eps) * w, all in float32
 (reference src/layers/ops/layernorm.py:50-88).  The reference adds residuals
 with a separate ``+`` in the model's dtype (src/models/qwen3/model.py:291, 296);
 here the stream is float32 and the add happens inside the norm kernel.
+
+``weight_offset``: a design may store the scale around zero and multiply by
+(offset + w); the sum is formed once, in float32, when the weights are loaded.
 """
 from __future__ import annotations
 
@@ -13,24 +16,28 @@ from typing import Optional
 import torch
 
 from .. import ops
-from ..weights.spec import NORM, WeightSpec
+from ..weights.spec import NORM, NORM_ZERO, WeightSpec
 from .base import Norm, StepContext, register
 
 
 @register("norm", "rmsnorm")
 class RMSNorm(Norm):
-    def __init__(self, width: int, eps: float, weight_name: str = "weight"):
+    def __init__(self, width: int, eps: float, weight_name: str = "weight", weight_offset: float = 0.0):
         self.width = width
         self.eps = float(eps)
         self.weight_name = weight_name
+        self.weight_offset = float(weight_offset)
         self.weight: Optional[torch.Tensor] = None
 
     def weight_specs(self, prefix: str) -> list[WeightSpec]:
-        return [WeightSpec(prefix + self.weight_name, (self.width,), NORM)]
+        return [WeightSpec(prefix + self.weight_name, (self.width,), NORM_ZERO if self.weight_offset else NORM)]
 
     def load(self, prefix, source, dtype, device) -> None:
         # scale vectors are float32 on the device whatever the compute dtype
-        self.weight = source.get(prefix + self.weight_name).to(torch.float32).to(device).contiguous()
+        w = source.get(prefix + self.weight_name).to(torch.float32)
+        if self.weight_offset:
+            w = w + self.weight_offset
+        self.weight = w.to(device).contiguous()
 
     def normed(self, ctx: StepContext, stream, lazy: bool = False):
         x = ops.NormedInput(stream, self.weight, self.eps, ctx.arena.alloc, ctx.dtype)

@@ -11,8 +11,9 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Any, Callable
 
-from .config import ConfigError, ModelConfig, Qwen3Config, read_config_json
+from .config import ConfigError, GanidraConfig, ModelConfig, Qwen3Config, read_config_json
 from .models.decoder import DecoderModel, ModelLayout
+from .models.ganidra import ganidra_layout
 from .models.qwen3 import qwen3_layout
 
 
@@ -31,12 +32,15 @@ def register_architecture(name: str, config_class: type, layout: Callable[[Any],
 
 
 register_architecture("Qwen3ForCausalLM", Qwen3Config, qwen3_layout)
+register_architecture("Ganidra", GanidraConfig, ganidra_layout)
 
 
 def architecture_of(raw_config: dict[str, Any]) -> Architecture:
     names = raw_config.get("architectures")
+    if names is None and isinstance(raw_config.get("architecture"), str):
+        names = [raw_config["architecture"]]          # some designs name themselves with one string
     if not names or not isinstance(names, list):
-        raise ConfigError("config.json: 'architectures' is missing; known: "
+        raise ConfigError("config.json: 'architectures' (or 'architecture') is missing; known: "
                           f"{sorted(ARCHITECTURES)}")
     if names[0] not in ARCHITECTURES:
         raise ConfigError(f"config.json: architecture {names[0]!r} is not registered; known: "

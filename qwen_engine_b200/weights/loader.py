@@ -65,8 +65,8 @@ def check_against_manifest(source, manifest: Iterable[WeightSpec], where: str = 
     wrong = []
     for n in sorted(have & set(specs)):
         got, want = tuple(source.shape(n)), tuple(specs[n].shape)
-        if got != want and not specs[n].optional:
-            wrong.append(f"{n}: stored {list(got)}, model needs {list(want)}")
+        if not specs[n].fits(got) and not specs[n].optional:
+            wrong.append(f"{n}: stored {list(got)}, model needs {['any' if d is None else d for d in want]}")
     if not (missing or unexpected or wrong):
         return
     lines = [f"{where} does not fit the model:"]

@@ -16,7 +16,7 @@ import torch
 from safetensors.torch import save_file
 
 from ..config import ModelConfig, write_config_json
-from .spec import MATRIX, NORM, WeightSpec
+from .spec import MATRIX, NORM, NORM_ZERO, VECTOR, WeightSpec
 
 
 def _tensor_seed(seed: int, name: str) -> int:
@@ -27,7 +27,8 @@ def _tensor_seed(seed: int, name: str) -> int:
 class RandomSource:
     """A TensorSource that makes each tensor when asked.
 
-    Matrices are N(0, std); norm scales are 1 + N(0, norm_std).  Values are drawn
+    Matrices are N(0, std); norm scales are 1 + N(0, norm_std), or N(0, norm_std) where the norm
+    adds the one itself; biases are N(0, 1).  Values are drawn
     in float32 on the CPU and rounded to ``store_dtype``."""
 
     def __init__(self, manifest: Iterable[WeightSpec], seed: int, std: float = 0.02,
@@ -40,14 +41,18 @@ class RandomSource:
         return self._specs.keys()
 
     def shape(self, name: str) -> tuple[int, ...]:
-        return tuple(self._specs[name].shape)
+        return self._specs[name].drawn_shape
 
     def get(self, name: str) -> torch.Tensor:
         spec = self._specs[name]
         gen = torch.Generator(device="cpu").manual_seed(_tensor_seed(self.seed, name))
-        t = torch.randn(spec.shape, generator=gen, dtype=torch.float32)
+        t = torch.randn(spec.drawn_shape, generator=gen, dtype=torch.float32)
         if spec.kind == NORM:
             t = 1.0 + self.norm_std * t
+        elif spec.kind == NORM_ZERO:
+            t = self.norm_std * t
+        elif spec.kind == VECTOR:
+            pass                                     # a bias: N(0, 1), so that what it feeds (a decay) varies
         elif spec.kind == MATRIX:
             t = self.std * t
         else:

@@ -21,12 +21,18 @@ def prepare_matrix(w):
     return w.contiguous()
 
 
-def embedding(token_ids, table, out, ssq=None):
+def embedding(token_ids, table, out, ssq=None, scale=1.0, accumulate=False):
     from qwen_engine_b200.ops import ResidualStream
     if isinstance(out, ResidualStream):
-        out.has_delta, out.n_ssq = False, 0
+        if not accumulate:
+            out.has_delta = False
+        out.n_ssq = 0
         out = out.resid
-    out.copy_(table[token_ids.long()].to(torch.float32))
+    rows = table[token_ids.long()].to(torch.float32) * scale
+    if accumulate:
+        out.add_(rows)
+    else:
+        out.copy_(rows)
 
 
 def _rms(x, weight, eps):
@@ -81,16 +87,17 @@ def rope_table(positions, inv_freq, out):
 
 
 def qk_norm_rope_kv_write(qkv, positions, q_norm_w, k_norm_w, eps, inv_freq, rotary_dim, kv_pages,
-                          slot_mapping, num_heads, num_kv_heads, head_dim, write_kv=True, cos_sin=None):
+                          slot_mapping, num_heads, num_kv_heads, head_dim, write_kv=True, cos_sin=None, norm_dim=None):
     T = qkv.shape[0]
     Hq, Hkv, D = num_heads, num_kv_heads, head_dim
     q = qkv[:, :Hq * D].reshape(T, Hq, D).to(torch.float32)
     k = qkv[:, Hq * D:(Hq + Hkv) * D].reshape(T, Hkv, D).to(torch.float32)
     v = qkv[:, (Hq + Hkv) * D:].reshape(T, Hkv, D)
+    n = norm_dim or D          # the mean runs over the head's own channels; the rest is zero padding
     if q_norm_w is not None:
-        q = _rms(q, q_norm_w, eps)
+        q = q * torch.rsqrt((q * q).sum(dim=-1, keepdim=True) / n + eps) * q_norm_w
     if k_norm_w is not None:
-        k = _rms(k, k_norm_w, eps)
+        k = k * torch.rsqrt((k * k).sum(dim=-1, keepdim=True) / n + eps) * k_norm_w
     if inv_freq is not None:
         q = _rotate(q, positions, inv_freq, rotary_dim)
         k = _rotate(k, positions, inv_freq, rotary_dim)
@@ -117,7 +124,8 @@ def plan_attention(q_lens, ctx_lens, page_size, geometries=(), dtype=None, unifo
     return {"tiles": tiles}
 
 
-def paged_attention(qkv, kv_pages, block_tables, ctx, out, scale, window, num_heads, num_kv_heads, head_dim, next_pages=None):
+def paged_attention(qkv, kv_pages, block_tables, ctx, out, scale, window, num_heads, num_kv_heads, head_dim, next_pages=None,
+                    slopes=None):
     """For each request: gather its keys and values from the pages by its block table, then
     softmax(scale q k^T + mask) v with key j allowed for the query at position i iff
     j <= i and (window == 0 or j > i - window)."""
@@ -149,6 +157,8 @@ def paged_attention(qkv, kv_pages, block_tables, ctx, out, scale, window, num_he
         v = torch.where(needed[:, None, None], v, torch.zeros_like(v))
         for h in range(Hq):
             s = (q[:, h, :] @ k[:, h // group, :].t()) * scale
+            if slopes is not None:
+                s = s - float(slopes[h]) * (qpos[:, None] - kpos[None, :]).to(torch.float32)
             s = s.masked_fill(~allowed, float("-inf"))
             p = torch.softmax(s, dim=-1)
             out[a:b, h * D:(h + 1) * D] = (p @ v[:, h // group, :]).to(out.dtype)
@@ -159,6 +169,63 @@ def silu_mul(gate_up, out):
     g = gate_up[:, :I].to(torch.float32)
     u = gate_up[:, I:].to(torch.float32)
     out.copy_((g / (1.0 + torch.exp(-g)) * u).to(out.dtype))
+
+
+def act_mul(gate_up, out, activation="silu"):
+    import math
+    I = out.shape[1]
+    g = gate_up[:, :I].to(torch.float32)
+    u = gate_up[:, I:].to(torch.float32)
+    if activation == "silu":
+        a = g / (1.0 + torch.exp(-g))
+    elif activation == "gelu_tanh":
+        a = 0.5 * g * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (g + 0.044715 * g ** 3)))
+    else:
+        raise ValueError(activation)
+    out.copy_((a * u).to(out.dtype))
+
+
+def channel_decay(a, w, bias, tau, out):
+    z = a.to(torch.float32) @ w.to(torch.float32).t()
+    if bias is not None:
+        z = z + bias
+    out.copy_(torch.exp(torch.nn.functional.logsigmoid(z) / tau))
+
+
+def linear_attention_scan(q, k, v, alpha, state, ctx, out, q_scale, num_heads, key_dim, value_dim, write_state=True):
+    """state [slots, H, dv, dk]; per request and head, token by token."""
+    H, dk, dv = num_heads, key_dim, value_dim
+    cu, ctx_lens, slots = ctx.cu_q.tolist(), ctx.ctx_lens.tolist(), ctx.slot_ids.tolist()
+    for r in range(len(ctx_lens)):
+        a, b = cu[r], cu[r + 1]
+        if b <= a:
+            continue
+        S = state[slots[r]].clone() if ctx_lens[r] > 0 else torch.zeros_like(state[slots[r]])     # [H, dv, dk]
+        for t in range(a, b):
+            qt = q[t].to(torch.float32).reshape(H, dk) * q_scale
+            kt = k[t].to(torch.float32).reshape(H, dk)
+            vt = v[t].to(torch.float32).reshape(H, dv)
+            at = alpha[t].reshape(H, dk)
+            S = S * at[:, None, :] + vt[:, :, None] * kt[:, None, :]
+            out[t] = (S * qt[:, None, :]).sum(dim=-1).reshape(H * dv)
+        if write_state:
+            state[slots[r]] = S
+
+
+def head_norm_gate(x, gate, weight, eps, out, num_heads, head_dim, gate_kind="silu", scale=1.0):
+    T = x.shape[0]
+    y = x.to(torch.float32).reshape(T, num_heads, head_dim)
+    if weight is not None:
+        y = y * torch.rsqrt((y * y).mean(dim=-1, keepdim=True) + eps) * weight
+    if gate is not None:
+        g = gate.to(torch.float32).reshape(T, num_heads, head_dim)
+        y = y * (g / (1.0 + torch.exp(-g)) if gate_kind == "silu" else torch.sigmoid(g))
+    out.copy_((y * scale).reshape(T, num_heads * head_dim).to(out.dtype))
+
+
+def scaled_add(acc, x, scale, first=False):
+    base = torch.zeros_like(acc, dtype=torch.float32) if first else acc.to(torch.float32)
+    acc.copy_((base + scale * x.to(torch.float32)).to(acc.dtype))
 
 
 def linear_silu_mul(gate_up, w, out, scratch):
@@ -215,7 +282,7 @@ def copy_pages(cache, pairs):
         cache[:, dst] = cache[:, src].clone()
 
 
-_NAMES = ["copy_pages", "swiglu_small_applies", "qkv_rope_small_applies", "prepare_matrix", "embedding", "add_rmsnorm", "add_rmsnorm_rows", "linear",
+_NAMES = ["act_mul", "channel_decay", "linear_attention_scan", "head_norm_gate", "scaled_add", "copy_pages", "swiglu_small_applies", "qkv_rope_small_applies", "prepare_matrix", "embedding", "add_rmsnorm", "add_rmsnorm_rows", "linear",
           "qk_norm_rope_kv_write", "rope_neox", "rope_table", "place_tokens", "swiglu_fused_applies", "plan_attention", "paged_attention", "silu_mul", "linear_silu_mul",
           "argmax", "sample"]
 
