@@ -449,6 +449,156 @@ def run_workload(name: str, torch, peaks) -> dict:
     return rec
 
 
+# ---- two designs side by side ---------------------------------------------------------------------------------------------
+# Sizes that resemble real models' layers.  A Ganidra model alternates a layer with a gated-linear-attention mixer and a
+# layer with windowed softmax attention beside such a mixer, each with its gated feed-forward; the Qwen3 model beside it
+# has the same width, feed-forward, heads and number of layers.
+COMPARE_SIZES = {
+    "w1024": dict(width=1024, ff=3072, heads=16, kv_heads=8, head_dim=128, gla_heads=8, gla_dk=64, gla_dv=128, window=1024,
+                  layers=8, vocab=32768, preset="qwen3-0.6b"),
+    "w2048": dict(width=2048, ff=6144, heads=16, kv_heads=8, head_dim=128, gla_heads=16, gla_dk=64, gla_dv=128, window=1024,
+                  layers=8, vocab=32768, preset="qwen3-1.7b"),
+}
+_TIMED_OPS = ("embedding", "linear", "linear_swiglu", "linear_swiglu_small", "linear_silu_mul", "linear_qkv_rope", "act_mul",
+              "qk_norm_rope_kv_write", "paged_attention", "channel_decay", "linear_attention_scan", "head_norm_gate",
+              "add_rmsnorm", "add_rmsnorm_rows", "rope_table")
+
+
+def ganidra_config_of(sz: dict) -> dict:
+    gla = dict(heads=sz["gla_heads"], dim=sz["gla_dk"], vdim=sz["gla_dv"], tau=16.0, rank=16)
+    left = dict(heads=sz["heads"], kv_heads=sz["kv_heads"], dim=sz["head_dim"], vdim=sz["head_dim"],
+                mask=dict(size=sz["window"]), scale=sz["head_dim"] ** -0.5)
+    mlp = dict(kind="dense", ff=sz["ff"])
+    pair = [dict(type="gla", mixer=gla, mlp=mlp),
+            dict(type="parallel", mixer=dict(left=left, right=dict(gla, heads=max(1, sz["gla_heads"] // 2)),
+                                             left_scale=0.7, right_scale=0.7), mlp=mlp)]
+    return dict(architecture="Ganidra", vocab=sz["vocab"], width=sz["width"], embedding=dict(scale=1.0), norm=dict(eps=1e-6),
+                layers=pair * (sz["layers"] // 2), loop=dict(start=0, stop=0, times=1))
+
+
+def compare_designs(args) -> int:
+    """``--compare ganidra``: prefill and decode of a Ganidra model beside a Qwen3 model of equal sizes (random weights,
+    bfloat16), and the device time of every class of operation in one eager step of each (CUDA events around every
+    call, the calls of a class added up).  Prints one JSON line."""
+    import torch
+    from qwen_engine_b200 import ops
+    from qwen_engine_b200.config import preset_config_dict
+    from qwen_engine_b200.engine.loading import load_model
+    from qwen_engine_b200.engine.runner import StepEntry
+    from qwen_engine_b200.registry import config_from_dict
+    peaks, peaks_src = load_peaks()
+    P, B, C = args.prefill_tokens, args.batch, args.context
+    page = 16
+    rng = random.Random(0)
+    clocks = ClockSampler()
+    clocks.start()
+    m_start = clocks.mark()
+
+    def events_time(fn, n):
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / n
+
+    def by_operation(runner, entries_fn):
+        """Device microseconds by class of operation in one eager step."""
+        spans = []
+        saved = {name: getattr(ops, name) for name in _TIMED_OPS}
+
+        def wrap(name, fn):
+            def timed_call(*a, **k):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                r = fn(*a, **k)
+                e1.record()
+                spans.append((name, e0, e1))
+                return r
+            return timed_call
+        graphs = runner.use_cuda_graphs
+        runner.use_cuda_graphs = False
+        for name, fn in saved.items():
+            setattr(ops, name, wrap(name, fn))
+        try:
+            runner.step(entries_fn())
+            torch.cuda.synchronize()
+        finally:
+            for name, fn in saved.items():
+                setattr(ops, name, fn)
+            runner.use_cuda_graphs = graphs
+        out: dict = {}
+        for name, e0, e1 in spans:
+            rec = out.setdefault(name, {"calls": 0, "us": 0.0})
+            rec["calls"] += 1
+            rec["us"] += e0.elapsed_time(e1) * 1e3
+        return {k: {"calls": v["calls"], "us": round(v["us"], 1)} for k, v in sorted(out.items(), key=lambda kv: -kv[1]["us"])}
+
+    def measure(cfg, tag):
+        V = cfg.vocab_size
+        pages = (B + 1) * (-(-(C + 64 * (args.steps + args.warmup + 8)) // page) + 1) + -(-P // page) + 8
+        loaded = load_model(None, torch.bfloat16, "cuda:0", page, pages, B + 2, enable_prefix_cache=False, config=cfg,
+                            random_seed=2, random_std=0.02, random_norm_std=0.1)
+        runner, cache = loaded.runner, loaded.cache
+        toks = lambda n: [rng.randrange(V) for _ in range(n)]
+        prompt = toks(P)
+
+        def prefill_once():
+            rc = cache.open("p")
+            runner.step([StepEntry(rc, prompt, [P - 1])])
+            cache.close(rc)
+        for _ in range(args.warmup):
+            prefill_once()
+        prefill_ms = events_time(prefill_once, 5)
+
+        def prefill_entries():
+            rc = cache.open("p")
+            return [StepEntry(rc, prompt, [P - 1])]
+        prefill_ops = by_operation(runner, prefill_entries)
+        cache.close(cache.live["p"])
+        reqs = [cache.open(f"d{i}") for i in range(B)]
+        for i in range(0, B, max(1, 4096 // C)):
+            runner.step([StepEntry(rc, toks(C), []) for rc in reqs[i:i + max(1, 4096 // C)]])
+        one = lambda: runner.step([StepEntry(rc, [rng.randrange(V)], [0]) for rc in reqs])
+        for _ in range(args.warmup):
+            one()
+        decode_ms = events_time(one, args.steps)
+        decode_ops = by_operation(runner, lambda: [StepEntry(rc, [rng.randrange(V)], [0]) for rc in reqs])
+        for rc in reqs:
+            cache.close(rc)
+        weight_bytes = loaded.model.weight_bytes()
+        state_bytes = sum(g.tensor[:, 0].numel() * g.tensor.element_size() for g in cache.groups if not g.is_paged)
+        rec = {"layers": len(loaded.model.layout.plan), "weight_mb": round(weight_bytes / 2**20, 1),
+               "prefill": {"tokens": P, "ms": round(prefill_ms, 3), "tokens_per_s": round(P / prefill_ms * 1e3, 1)},
+               "decode": {"batch": B, "context": C, "ms": round(decode_ms, 4), "tokens_per_s": round(B / decode_ms * 1e3, 1)},
+               "state_bytes_per_request": state_bytes, "prefill_ops_us": prefill_ops, "decode_ops_us": decode_ops}
+        ops.check_device_status()
+        del loaded, runner, cache, reqs
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        return rec
+
+    out = {}
+    for name in ([args.compare_size] if args.compare_size else list(COMPARE_SIZES)):
+        sz = COMPARE_SIZES[name]
+        qraw = preset_config_dict(sz["preset"])
+        qraw.update(num_hidden_layers=sz["layers"], vocab_size=sz["vocab"])
+        out[name] = {"sizes": sz, "ganidra": measure(config_from_dict(ganidra_config_of(sz)), "ganidra"),
+                     "qwen3": measure(config_from_dict(qraw), "qwen3")}
+        g, q = out[name]["ganidra"], out[name]["qwen3"]
+        out[name]["ganidra_over_qwen3"] = {"prefill": round(g["prefill"]["tokens_per_s"] / q["prefill"]["tokens_per_s"], 3),
+                                           "decode": round(g["decode"]["tokens_per_s"] / q["decode"]["tokens_per_s"], 3)}
+    clocks.stop()
+    print(json.dumps({"metric": "prefill and decode tok/s, Ganidra beside Qwen3 at equal sizes", "impl": "ours", "n_gpus": 1,
+                      "dtype": "bf16", "data": "synthetic: uniform random token ids, random weights N(0, 0.02) seed 2",
+                      "steps": args.steps, "warmup": args.warmup, "peaks": peaks_src, "sizes": out,
+                      "clocks": clocks.summary([(m_start, clocks.mark())])}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -470,6 +620,10 @@ def main() -> int:
     ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel-class timings")
     ap.add_argument("--profile", choices=["decode", "prefill"], default=None,
                     help="bracket that timed region with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
+    ap.add_argument("--compare", choices=["ganidra"], default=None,
+                    help="instead of the default workload: prefill and decode of a Ganidra model beside a Qwen3 model of equal "
+                         "sizes, with the device time of every class of operation (one JSON line)")
+    ap.add_argument("--compare-size", choices=sorted(COMPARE_SIZES), default=None, help="with --compare: one size only")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -477,6 +631,8 @@ def main() -> int:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     args.warmup = max(args.warmup, 3)
+    if args.compare:
+        return compare_designs(args)
 
     import torch
     from qwen_engine_b200 import ops

@@ -98,6 +98,7 @@ struct GlaArgs {
   float* out;                                         // [T, H * dv]
   float q_scale;
   int H, dk, dv, L, VT, chunk, write_state;
+  int vec;                                            // q, k, v, alpha can be staged in pieces of 16 bytes
 };
 
 // index of key channel c in a staged row: blocks of DC channels, 4 floats of padding between them (banks)
@@ -152,7 +153,8 @@ gla_scan_kernel(GlaArgs A) {
   const int ptid = tid - n_compute, n_prod = blockDim.x - n_compute;
   const int padded = L * DC;
 
-  // stage chunk `ch` into buf[ch & 1]: by the producers, or by everybody for the first chunk
+  // stage chunk `ch` into buf[ch & 1], element by element (any sizes and strides): by the producers, or by everybody
+  // for the first chunk
   auto stage = [&](int ch, int t_id, int t_n) {
     float* b = buf[ch & 1];
     const int t_first = ch * A.chunk;
@@ -177,34 +179,125 @@ gla_scan_kernel(GlaArgs A) {
     }
   };
 
-  stage(0, tid, blockDim.x);
+  // The same in pieces of 16 bytes where sizes, strides and addresses allow (A.vec): a thread's pieces of a chunk sit
+  // at the same places in every chunk, so their offsets are worked out once; all of a thread's loads are on their way
+  // before the first is converted and stored.
+  constexpr int VEC = 16 / (int)sizeof(T);             // elements of q, k, v in a piece
+  constexpr int NI = 8;                                // pieces a thread has on their way at a time
+  const int pieces_qk = dk / VEC, pieces_a = dk / 4, pieces_v = VT / VEC;
+  const int per_tok_v = 2 * pieces_qk + pieces_a + pieces_v;
+  auto stage_vec = [&](int ch, int t_id, int t_n) {
+    float* b = buf[ch & 1];
+    const int t_first = ch * A.chunk;
+    const int rows = min(A.chunk, n - t_first);
+    const int total = rows * per_tok_v;
+    const size_t base_row = (size_t)(row0 + t_first);
+    for (int e0 = t_id; e0 < total; e0 += NI * t_n) {
+      uint4 r[NI];
+      int so[NI], so2[NI], kind[NI];        // where a piece's first and second four channels go
+#pragma unroll
+      for (int i = 0; i < NI; ++i) {
+        const int e = e0 + i * t_n;
+        kind[i] = -1;
+        if (e < total) {
+          const int t = e / per_tok_v;
+          int x = e - t * per_tok_v;
+          const size_t row = base_row + t;
+          const void* src;
+          if (x < pieces_qk) {
+            kind[i] = 0; src = q + row * A.ldq + x * VEC;
+            so[i] = t * tok_w + gla_pad<DC>(x * VEC); so2[i] = t * tok_w + gla_pad<DC>(x * VEC + 4);
+          } else if ((x -= pieces_qk) < pieces_qk) {
+            kind[i] = 1; src = k + row * A.ldk + x * VEC;
+            so[i] = t * tok_w + row_w + gla_pad<DC>(x * VEC); so2[i] = t * tok_w + row_w + gla_pad<DC>(x * VEC + 4);
+          } else if ((x -= pieces_qk) < pieces_a) {
+            kind[i] = 2; src = al + row * ((size_t)H * dk) + x * 4;
+            so[i] = so2[i] = t * tok_w + 2 * row_w + gla_pad<DC>(x * 4);
+          } else {
+            x -= pieces_a; kind[i] = 3; src = v + row * A.ldv + j0 + x * VEC;
+            so[i] = t * tok_w + 3 * row_w + x * VEC; so2[i] = so[i] + 4;
+            if (j0 + x * VEC >= dv) src = nullptr;                 // the last tile's columns beyond the head: zeros
+          }
+          r[i] = src ? __ldg(reinterpret_cast<const uint4*>(src)) : make_uint4(0, 0, 0, 0);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < NI; ++i) {
+        if (kind[i] < 0) continue;
+        float* dst = b + so[i];
+        if (kind[i] == 2) { *reinterpret_cast<uint4*>(dst) = r[i]; continue; }
+        float f[VEC];
+        if constexpr (sizeof(T) == 2) {
+          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&r[i]);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) { const float2 x2 = __bfloat1622float2(h2[u]); f[2 * u] = x2.x; f[2 * u + 1] = x2.y; }
+        } else {
+          f[0] = __uint_as_float(r[i].x); f[1] = __uint_as_float(r[i].y); f[2] = __uint_as_float(r[i].z); f[3] = __uint_as_float(r[i].w);
+        }
+        if (kind[i] == 0) {
+#pragma unroll
+          for (int u = 0; u < VEC; ++u) f[u] *= A.q_scale;
+        }
+        // groups of four channels never straddle a thread's block of DC (a multiple of four): the padding falls between
+        *reinterpret_cast<float4*>(dst) = make_float4(f[0], f[1], f[2], f[3]);
+        if constexpr (VEC == 8) *reinterpret_cast<float4*>(b + so2[i]) = make_float4(f[4], f[5], f[6], f[7]);
+      }
+    }
+  };
+
+  if (A.vec) {
+    // channels beyond the head (L * DC > dk) are never staged by pieces: nothing in, nothing kept, nothing out
+    if (padded > dk)
+      for (int e = tid; e < 2 * A.chunk * (padded - dk); e += blockDim.x) {
+        const int t = e / (padded - dk), c = dk + e - t * (padded - dk);
+        float* dst = smem + (size_t)t * tok_w + gla_pad<DC>(c);
+        dst[0] = 0.f; dst[row_w] = 0.f; dst[2 * row_w] = 1.f;
+      }
+    stage_vec(0, tid, blockDim.x);
+  } else {
+    stage(0, tid, blockDim.x);
+  }
   __syncthreads();
   for (int ch = 0; ch < n_chunks; ++ch) {
     if (producer) {
-      if (ch + 1 < n_chunks) stage(ch + 1, ptid, n_prod);
+      if (ch + 1 < n_chunks) { if (A.vec) stage_vec(ch + 1, ptid, n_prod); else stage(ch + 1, ptid, n_prod); }
     } else if (owns) {
       const float* b = buf[ch & 1];
       const int rows = min(A.chunk, n - ch * A.chunk);
       float* o = A.out + (size_t)(row0 + ch * A.chunk) * ((size_t)H * dv) + (size_t)head * dv + j;
-      for (int t = 0; t < rows; ++t) {
-        const float* r = b + (size_t)t * tok_w;
-        const float* rq = r + l * (DC + 4);
-        const float* rk = rq + row_w;
-        const float* ra = rk + row_w;
-        const float vj = r[3 * row_w + (j - j0)];
-        float acc = 0.f;
+      // four tokens a turn: the state's chain runs through them one after the other, their sums over the column's
+      // threads meet side by side
+      for (int t0 = 0; t0 < rows; t0 += 4) {
+        float acc[4];
 #pragma unroll
-        for (int i = 0; i < DC; i += 4) {
-          const float4 q4 = *reinterpret_cast<const float4*>(rq + i);
-          const float4 k4 = *reinterpret_cast<const float4*>(rk + i);
-          const float4 a4 = *reinterpret_cast<const float4*>(ra + i);
-          s[i] = fmaf(a4.x, s[i], k4.x * vj);             acc = fmaf(q4.x, s[i], acc);
-          s[i + 1] = fmaf(a4.y, s[i + 1], k4.y * vj);     acc = fmaf(q4.y, s[i + 1], acc);
-          s[i + 2] = fmaf(a4.z, s[i + 2], k4.z * vj);     acc = fmaf(q4.z, s[i + 2], acc);
-          s[i + 3] = fmaf(a4.w, s[i + 3], k4.w * vj);     acc = fmaf(q4.w, s[i + 3], acc);
+        for (int u = 0; u < 4; ++u) {
+          acc[u] = 0.f;
+          if (t0 + u < rows) {
+            const float* r = b + (size_t)(t0 + u) * tok_w;
+            const float* rq = r + l * (DC + 4);
+            const float* rk = rq + row_w;
+            const float* ra = rk + row_w;
+            const float vj = r[3 * row_w + (j - j0)];
+#pragma unroll
+            for (int i = 0; i < DC; i += 4) {
+              const float4 q4 = *reinterpret_cast<const float4*>(rq + i);
+              const float4 k4 = *reinterpret_cast<const float4*>(rk + i);
+              const float4 a4 = *reinterpret_cast<const float4*>(ra + i);
+              s[i] = fmaf(a4.x, s[i], k4.x * vj);             acc[u] = fmaf(q4.x, s[i], acc[u]);
+              s[i + 1] = fmaf(a4.y, s[i + 1], k4.y * vj);     acc[u] = fmaf(q4.y, s[i + 1], acc[u]);
+              s[i + 2] = fmaf(a4.z, s[i + 2], k4.z * vj);     acc[u] = fmaf(q4.z, s[i + 2], acc[u]);
+              s[i + 3] = fmaf(a4.w, s[i + 3], k4.w * vj);     acc[u] = fmaf(q4.w, s[i + 3], acc[u]);
+            }
+          }
         }
-        for (int off = L >> 1; off > 0; off >>= 1) acc += __shfl_xor_sync(col_mask, acc, off);
-        if (l == 0) o[(size_t)t * ((size_t)H * dv)] = acc;
+        for (int off = L >> 1; off > 0; off >>= 1) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) acc[u] += __shfl_xor_sync(col_mask, acc[u], off);
+        }
+        if (l == 0) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) if (t0 + u < rows) o[(size_t)(t0 + u) * ((size_t)H * dv)] = acc[u];
+        }
       }
     }
     __syncthreads();
@@ -272,6 +365,10 @@ extern "C" int qe_linear_attention_scan(const void* q, const void* k, const void
   int chunk = max_q_len < 16 ? (max_q_len < 1 ? 1 : max_q_len) : 16;
   while (chunk > 1 && (size_t)2 * chunk * tok_w * sizeof(float) > 96 * 1024) chunk >>= 1;
   A.chunk = chunk;
+  // pieces of 16 bytes: whole pieces per head and per tile of value channels, rows and bases on 16-byte boundaries
+  const int vec_n = dtype == QE_DTYPE_F32 ? 4 : 8;
+  A.vec = dk % vec_n == 0 && dk % 4 == 0 && VT % vec_n == 0 && dv % vec_n == 0 && ldq % vec_n == 0 && ldk % vec_n == 0 &&
+          ldv % vec_n == 0 && (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)alpha) & 15) == 0;
   const size_t smem = (size_t)2 * chunk * tok_w * sizeof(float);
   if (smem > 96 * 1024) QE_REFUSE("linear_attention_scan: key size %d needs %zu bytes of shared memory", dk, smem);
 #define GLA_CASE(TT, DCC) return gla_launch<TT, DCC>(A, R, stream, smem)
