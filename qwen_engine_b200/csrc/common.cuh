@@ -51,6 +51,18 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return scratch[32];
 }
 
+// The gate's activation where a feed-forward's gate/up product forms act(gate) * up in its own epilogue (bfloat16
+// results): 0 silu, g / (1 + exp(-g)); 1 the tanh form of gelu, 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))).
+// Float32 arithmetic with the hardware's exponential, quotient and tanh; the product is rounded once.
+__device__ __forceinline__ float gate_act_fast(float g, int act) {
+  if (act == 1) {
+    float t;
+    asm("tanh.approx.f32 %0, %1;\n" : "=f"(t) : "f"(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    return 0.5f * g * (1.f + t);
+  }
+  return __fdividef(g, 1.f + __expf(-g));
+}
+
 // ---- programmatic dependent launch --------------------------------------------------------------------
 // Kernels of a step form a chain on one stream.  Launched with the attribute below, a kernel may
 // start while its predecessor is still running; it must call pdl_wait() before it touches anything

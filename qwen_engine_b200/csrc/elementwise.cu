@@ -281,7 +281,7 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
 }
 
 __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out,
-                                       int I, size_t total8) {
+                                       int I, size_t total8, int act) {
   pdl_launch_dependents();
   pdl_wait();
   // two 16-byte pieces per thread and turn, all four loads in flight before the arithmetic; the
@@ -301,13 +301,13 @@ __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up
     bf16x8_to_f32(rg0, g);
     bf16x8_to_f32(ru0, u);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) g[k] = __fdividef(g[k], 1.f + __expf(-g[k])) * u[k];
+    for (int k = 0; k < 8; ++k) g[k] = gate_act_fast(g[k], act) * u[k];
     *reinterpret_cast<uint4*>(out + t0 * I + i0) = f32_to_bf16x8(g);
     if (two) {
       bf16x8_to_f32(rg1, g);
       bf16x8_to_f32(ru1, u);
 #pragma unroll
-      for (int k = 0; k < 8; ++k) g[k] = __fdividef(g[k], 1.f + __expf(-g[k])) * u[k];
+      for (int k = 0; k < 8; ++k) g[k] = gate_act_fast(g[k], act) * u[k];
       *reinterpret_cast<uint4*>(out + t1 * I + i1) = f32_to_bf16x8(g);
     }
   }
@@ -324,11 +324,11 @@ extern "C" int qe_act_mul(const void* gate_up, void* out, int T, int I, int dtyp
 static int act_mul_launch(const void* gate_up, void* out, int T, int I, int dtype, int act, cudaStream_t stream) {
   if (T <= 0) return 0;
   const size_t total = (size_t)T * I;
-  if (act == 0 && dtype == QE_DTYPE_BF16 && I % 8 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0) {
+  if (dtype == QE_DTYPE_BF16 && I % 8 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0) {
     const size_t total8 = total / 8;
     const int vblocks = (int)((total8 + 255) / 256 < 148 * 8 ? (total8 + 255) / 256 : 148 * 8);
     qe_launch(silu_mul_bf16x8_kernel, dim3(vblocks), dim3(256), 0, stream, (const __nv_bfloat16*)gate_up,
-              (__nv_bfloat16*)out, I, total8);
+              (__nv_bfloat16*)out, I, total8, act);
     QE_CHECK_LAUNCH("silu_mul");
     return 0;
   }

@@ -288,7 +288,7 @@ extern "C" int qe_linear_small_m_norm(const float* resid, const float* ssq, int 
 template <int MT>
 __global__ void __launch_bounds__(512)
 gemm_small_m_swiglu_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
-                           __nv_bfloat16* __restrict__ act, int M, int I, int K, int k_per_warp, FuseArgs na) {
+                           __nv_bfloat16* __restrict__ act, int M, int I, int K, int k_per_warp, FuseArgs na, int gate_act) {
   extern __shared__ float red[];                    // 2 x [warps][16][8 MT]
   if (na.next_bytes) {
     const unsigned long long pieces = (na.next_bytes + 4095) >> 12;
@@ -300,12 +300,13 @@ gemm_small_m_swiglu_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloa
     }
   }
   pdl_launch_dependents();
-  gsm_cta_swiglu<MT>(x, w, act, M, I, K, k_per_warp, blockIdx.x, red);     // (waits for the kernel before it once its first weights are on their way)
+  gsm_cta_swiglu<MT>(x, w, act, M, I, K, k_per_warp, blockIdx.x, red, gate_act);     // (waits for the kernel before it once its first weights are on their way)
 }
 
 // act[M, I] = silu(x · w[:I]^T) * (x · w[I:]^T) for the stacked weights w [2 I, K], M <= 16 rows, bfloat16: a CTA
 // takes the gate rows and the up rows of the same 16 columns, so the activation never exists as gate and up in memory.
-extern "C" int qe_linear_small_m_swiglu(const void* x, const void* w, void* act, int M, int I, int K, cudaStream_t stream) {
+// gate_act: 0 silu, 1 the tanh form of gelu.
+extern "C" int qe_linear_small_m_swiglu(const void* x, const void* w, void* act, int M, int I, int K, int gate_act, cudaStream_t stream) {
   FuseArgs na{};
   na.next_w = g_next_w;
   na.next_bytes = g_next_bytes;
@@ -331,10 +332,10 @@ extern "C" int qe_linear_small_m_swiglu(const void* x, const void* w, void* act,
   }
   if (MT == 1)
     qe_launch(gemm_small_m_swiglu_kernel<1>, dim3(ctas), dim3(warps * 32), smem, stream, (const __nv_bfloat16*)x,
-              (const __nv_bfloat16*)w, (__nv_bfloat16*)act, M, I, K, k_per_warp, na);
+              (const __nv_bfloat16*)w, (__nv_bfloat16*)act, M, I, K, k_per_warp, na, gate_act);
   else
     qe_launch(gemm_small_m_swiglu_kernel<2>, dim3(ctas), dim3(warps * 32), smem, stream, (const __nv_bfloat16*)x,
-              (const __nv_bfloat16*)w, (__nv_bfloat16*)act, M, I, K, k_per_warp, na);
+              (const __nv_bfloat16*)w, (__nv_bfloat16*)act, M, I, K, k_per_warp, na, gate_act);
   QE_CHECK_LAUNCH("linear_small_m_swiglu");
   return 0;
 }

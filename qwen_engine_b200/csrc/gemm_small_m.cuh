@@ -325,7 +325,7 @@ __device__ __forceinline__ void gsm_cta(const __nv_bfloat16* __restrict__ x, con
 template <int MT>
 __device__ __forceinline__ void gsm_cta_swiglu(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                                                __nv_bfloat16* __restrict__ act, int M, int I, int K, int k_per_warp,
-                                               int vb, float* red) {
+                                               int vb, float* red, int gate_act = 0) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   const int g = lane >> 2, c = lane & 3;
   const int n0 = vb * 16;
@@ -404,7 +404,7 @@ __device__ __forceinline__ void gsm_cta_swiglu(const __nv_bfloat16* __restrict__
       su += red[((size_t)(nwarps + wi) * 16 + i) * MW + m];
     }
     const float gb = __bfloat162float(__float2bfloat16_rn(sg)), ub = __bfloat162float(__float2bfloat16_rn(su));
-    act[(size_t)m * I + n] = __float2bfloat16_rn(silu_fast(gb) * ub);
+    act[(size_t)m * I + n] = __float2bfloat16_rn(gate_act_fast(gb, gate_act) * ub);
   }
   QE_TL_MARK(3);
 }

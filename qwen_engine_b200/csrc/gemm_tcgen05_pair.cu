@@ -154,7 +154,7 @@ __device__ __forceinline__ void pr_meet_shares(const unsigned char* stg, TOut* _
 template <typename TOut, int BN, int STAGES, bool SWIGLU, bool ROPE = false>
 __global__ void __launch_bounds__(PR_THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                         TOut* __restrict__ out, int M, int N, int K, int n_up, PrRope rp, int splits) {
+                         TOut* __restrict__ out, int M, int N, int K, int n_up, PrRope rp, int splits, int gate_act) {
   static_assert(!SWIGLU || BN == 256, "the fused activation pairs 128 columns of gate with 128 of up");
   static_assert(!ROPE || (BN == 256 && !SWIGLU && sizeof(TOut) == 2), "the fused rotation takes two heads of 128 per tile, in bfloat16");
   extern __shared__ unsigned char smem_raw[];
@@ -328,8 +328,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
 #pragma unroll
             for (int j = 0; j < 32; j += 2) {
               const float g0 = __uint_as_float(g[q][j]), g1 = __uint_as_float(g[q][j + 1]);
-              __nv_bfloat162 pj = __floats2bfloat162_rn(__fdividef(g0, 1.f + __expf(-g0)) * __uint_as_float(u[q][j]),
-                                                        __fdividef(g1, 1.f + __expf(-g1)) * __uint_as_float(u[q][j + 1]));
+              __nv_bfloat162 pj = __floats2bfloat162_rn(gate_act_fast(g0, gate_act) * __uint_as_float(u[q][j]),
+                                                        gate_act_fast(g1, gate_act) * __uint_as_float(u[q][j + 1]));
               pk[16 * q + (j >> 1)] = *reinterpret_cast<uint32_t*>(&pj);
             }
           const int r_first = m0 + quarter * 32, c0 = ch * WC;
@@ -353,7 +353,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               const float gv = __uint_as_float(g[j]);
-              if (i0 + c0 + j < I) dst[j] = from_f32<TOut>(__fdividef(gv, 1.f + __expf(-gv)) * __uint_as_float(u[j]));
+              if (i0 + c0 + j < I) dst[j] = from_f32<TOut>(gate_act_fast(gv, gate_act) * __uint_as_float(u[j]));
             }
           }
         }
@@ -576,7 +576,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
 
 template <int BN, int STAGES, bool SWIGLU = false, bool ROPE = false>
 static int launch_pair(const void* x, const void* w, void* out, int M, int N, int K, int out_f32, int sms, cudaStream_t stream,
-                       PrRope rp = PrRope{}, int splits = 1) {
+                       PrRope rp = PrRope{}, int splits = 1, int gate_act = 0) {
   const int n_up = SWIGLU ? N / 2 : 0;
   CUtensorMap map_x, map_w;
   {
@@ -613,12 +613,12 @@ static int launch_pair(const void* x, const void* w, void* out, int M, int N, in
   const dim3 grid((unsigned)(2 * pairs));
   const unsigned cluster = 2u * (unsigned)splits;
   if constexpr (ROPE) {
-    qe_launch_cluster(gemm_tcgen05_pair_kernel<__nv_bfloat16, BN, STAGES, false, true>, grid, dim3(PR_THREADS), smem, stream, cluster, map_x, map_w, (__nv_bfloat16*)out, M, N, K, n_up, rp, 1);
+    qe_launch_cluster(gemm_tcgen05_pair_kernel<__nv_bfloat16, BN, STAGES, false, true>, grid, dim3(PR_THREADS), smem, stream, cluster, map_x, map_w, (__nv_bfloat16*)out, M, N, K, n_up, rp, 1, 0);
   } else {
     if (out_f32)
-      qe_launch_cluster(gemm_tcgen05_pair_kernel<float, BN, STAGES, SWIGLU, false>, grid, dim3(PR_THREADS), smem, stream, cluster, map_x, map_w, (float*)out, M, N, K, n_up, rp, splits);
+      qe_launch_cluster(gemm_tcgen05_pair_kernel<float, BN, STAGES, SWIGLU, false>, grid, dim3(PR_THREADS), smem, stream, cluster, map_x, map_w, (float*)out, M, N, K, n_up, rp, splits, gate_act);
     else
-      qe_launch_cluster(gemm_tcgen05_pair_kernel<__nv_bfloat16, BN, STAGES, SWIGLU, false>, grid, dim3(PR_THREADS), smem, stream, cluster, map_x, map_w, (__nv_bfloat16*)out, M, N, K, n_up, rp, splits);
+      qe_launch_cluster(gemm_tcgen05_pair_kernel<__nv_bfloat16, BN, STAGES, SWIGLU, false>, grid, dim3(PR_THREADS), smem, stream, cluster, map_x, map_w, (__nv_bfloat16*)out, M, N, K, n_up, rp, splits, gate_act);
   }
   QE_CHECK_LAUNCH("linear_tcgen05_pair");
   return 0;
@@ -724,15 +724,16 @@ extern "C" int qe_linear_tcgen05_pair(const void* x, const void* w, void* out, i
 
 // out[M, I] = silu(x · w[:I]^T) * (x · w[I:]^T) for the stacked gate and up weights w [2 I, K] (see SWIGLU
 // above).  Returns 0 when run, 1 when refused, 2 on a launch error.
+// gate_act: 0 silu, 1 the tanh form of gelu.
 extern "C" int qe_linear_swiglu_tcgen05_pair(const void* x, const void* w, void* out, int M, int I, int K, int out_f32,
-                                             cudaStream_t stream) {
+                                             int gate_act, cudaStream_t stream) {
   if (M <= 0 || I <= 0) return 0;
   if (K <= 0 || K % 8) QE_REFUSE("linear_swiglu: K = %d is not a positive multiple of 8", K);
   if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15) QE_REFUSE("linear_swiglu: operands must be 16-byte aligned");
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (sms < 2) QE_REFUSE("linear_swiglu: needs at least two SMs");
-  return launch_pair<256, 6, true>(x, w, out, M, 2 * I, K, out_f32, sms, stream);
+  return launch_pair<256, 6, true>(x, w, out, M, 2 * I, K, out_f32, sms, stream, PrRope{}, 1, gate_act);
 }
 
 // out[M, N] = the q columns of x · w^T for the stacked q, k, v weights w [N = (Hq + 2 Hkv) 128, K], normed per head

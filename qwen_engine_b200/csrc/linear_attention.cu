@@ -87,7 +87,7 @@ extern "C" int qe_channel_decay(const void* a, long lda, const void* w, const fl
 // the scan
 // ---------------------------------------------------------------------------------------------------------
 #define GLA_PRODUCERS 128          // threads that stage the next chunk
-#define GLA_MAX_COMPUTE 256        // threads that hold state
+#define GLA_MAX_COMPUTE 128        // threads that hold state (with the producers 256 a CTA: registers enough for eight tokens a turn)
 
 struct GlaArgs {
   const void* q; const void* k; const void* v;        // rows of the step's tokens; heads side by side
@@ -99,13 +99,16 @@ struct GlaArgs {
   float q_scale;
   int H, dk, dv, L, VT, chunk, write_state;
   int vec;                                            // q, k, v, alpha can be staged in pieces of 16 bytes
+  int fast;                                           // ... and a chunk is at most 8 pieces a producer
 };
 
 // index of key channel c in a staged row: blocks of DC channels, 4 floats of padding between them (banks)
 template <int DC> __device__ __forceinline__ int gla_pad(int c) { return c + (c / DC) * 4; }
 
-template <typename T, int DC>
-__global__ void __launch_bounds__(GLA_MAX_COMPUTE + GLA_PRODUCERS)
+// SINGLE: a step of single tokens (one chunk of one token a request): no producers, no turns of eight tokens, few
+// registers, many CTAs an SM.
+template <typename T, int DC, bool SINGLE>
+__global__ void __launch_bounds__(SINGLE ? GLA_MAX_COMPUTE : GLA_MAX_COMPUTE + GLA_PRODUCERS, SINGLE ? 4 : 1)
 gla_scan_kernel(GlaArgs A) {
   extern __shared__ float smem[];
   const int req = blockIdx.x, head = blockIdx.y, j0 = blockIdx.z * A.VT;
@@ -179,70 +182,104 @@ gla_scan_kernel(GlaArgs A) {
     }
   };
 
-  // The same in pieces of 16 bytes where sizes, strides and addresses allow (A.vec): a thread's pieces of a chunk sit
-  // at the same places in every chunk, so their offsets are worked out once; all of a thread's loads are on their way
-  // before the first is converted and stored.
+  // The same in pieces of 16 bytes where sizes, strides and addresses allow (A.vec).  A thread's pieces of a chunk sit
+  // at the same places in every chunk, so what describes them (which row of the chunk, where from, where to) is worked
+  // out once; all of a thread's loads are on their way before the first is converted and stored.
   constexpr int VEC = 16 / (int)sizeof(T);             // elements of q, k, v in a piece
   constexpr int NI = 8;                                // pieces a thread has on their way at a time
   const int pieces_qk = dk / VEC, pieces_a = dk / 4, pieces_v = VT / VEC;
   const int per_tok_v = 2 * pieces_qk + pieces_a + pieces_v;
+  // piece e of a chunk: token e / per_tok_v; then q, k, alpha, v in turn.  kind 0..3 (4: v columns beyond the head,
+  // zeros); `off`: bytes from the kind's base to the piece within its row; so, so2: where its two groups of four go
+  const char* const base_of[4] = {(const char*)q, (const char*)k, (const char*)al, (const char*)(v + j0)};
+  const long row_bytes_of[4] = {A.ldq * (long)sizeof(T), A.ldk * (long)sizeof(T), (long)H * dk * (long)sizeof(float),
+                                A.ldv * (long)sizeof(T)};
+  auto describe = [&](int e, int& t, int& off, int& so, int& so2, int& kind) {
+    t = e / per_tok_v;
+    int x = e - t * per_tok_v;
+    if (x < pieces_qk) {
+      kind = 0; off = x * 16;
+      so = t * tok_w + gla_pad<DC>(x * VEC); so2 = t * tok_w + gla_pad<DC>(x * VEC + 4);
+    } else if ((x -= pieces_qk) < pieces_qk) {
+      kind = 1; off = x * 16;
+      so = t * tok_w + row_w + gla_pad<DC>(x * VEC); so2 = t * tok_w + row_w + gla_pad<DC>(x * VEC + 4);
+    } else if ((x -= pieces_qk) < pieces_a) {
+      kind = 2; off = x * 16;
+      so = so2 = t * tok_w + 2 * row_w + gla_pad<DC>(x * 4);
+    } else {
+      x -= pieces_a;
+      kind = j0 + x * VEC >= dv ? 4 : 3; off = x * 16;
+      so = t * tok_w + 3 * row_w + x * VEC; so2 = so + 4;
+    }
+  };
+  auto fetch = [&](int kind, int off, size_t row) -> uint4 {
+    if (kind > 3) return make_uint4(0, 0, 0, 0);
+    const char* base = kind == 0 ? base_of[0] : kind == 1 ? base_of[1] : kind == 2 ? base_of[2] : base_of[3];
+    const long rb = kind == 0 ? row_bytes_of[0] : kind == 1 ? row_bytes_of[1] : kind == 2 ? row_bytes_of[2] : row_bytes_of[3];
+    return __ldg(reinterpret_cast<const uint4*>(base + row * rb + off));
+  };
+  auto put = [&](float* b, const uint4& r, int so, int so2, int kind) {
+    if (kind == 2) { *reinterpret_cast<uint4*>(b + so) = r; return; }      // (kinds 3 and 4 are values: no scale)
+    float f[VEC];
+    if constexpr (sizeof(T) == 2) {
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) { const float2 x2 = __bfloat1622float2(h2[u]); f[2 * u] = x2.x; f[2 * u + 1] = x2.y; }
+    } else {
+      f[0] = __uint_as_float(r.x); f[1] = __uint_as_float(r.y); f[2] = __uint_as_float(r.z); f[3] = __uint_as_float(r.w);
+    }
+    const float sc = kind == 0 ? A.q_scale : 1.f;
+    // groups of four channels never straddle a thread's block of DC (a multiple of four): the padding falls between
+    *reinterpret_cast<float4*>(b + so) = make_float4(f[0] * sc, f[1] * sc, f[2] * sc, f[3] * sc);
+    if constexpr (VEC == 8) *reinterpret_cast<float4*>(b + so2) = make_float4(f[4] * sc, f[5] * sc, f[6] * sc, f[7] * sc);
+  };
+  // any number of pieces, described as they come (the first chunk, by all threads; chunks too large for the fast form)
   auto stage_vec = [&](int ch, int t_id, int t_n) {
     float* b = buf[ch & 1];
     const int t_first = ch * A.chunk;
-    const int rows = min(A.chunk, n - t_first);
-    const int total = rows * per_tok_v;
-    const size_t base_row = (size_t)(row0 + t_first);
+    const int total = min(A.chunk, n - t_first) * per_tok_v;
     for (int e0 = t_id; e0 < total; e0 += NI * t_n) {
       uint4 r[NI];
-      int so[NI], so2[NI], kind[NI];        // where a piece's first and second four channels go
+      int so[NI], so2[NI], kind[NI];
 #pragma unroll
       for (int i = 0; i < NI; ++i) {
         const int e = e0 + i * t_n;
         kind[i] = -1;
         if (e < total) {
-          const int t = e / per_tok_v;
-          int x = e - t * per_tok_v;
-          const size_t row = base_row + t;
-          const void* src;
-          if (x < pieces_qk) {
-            kind[i] = 0; src = q + row * A.ldq + x * VEC;
-            so[i] = t * tok_w + gla_pad<DC>(x * VEC); so2[i] = t * tok_w + gla_pad<DC>(x * VEC + 4);
-          } else if ((x -= pieces_qk) < pieces_qk) {
-            kind[i] = 1; src = k + row * A.ldk + x * VEC;
-            so[i] = t * tok_w + row_w + gla_pad<DC>(x * VEC); so2[i] = t * tok_w + row_w + gla_pad<DC>(x * VEC + 4);
-          } else if ((x -= pieces_qk) < pieces_a) {
-            kind[i] = 2; src = al + row * ((size_t)H * dk) + x * 4;
-            so[i] = so2[i] = t * tok_w + 2 * row_w + gla_pad<DC>(x * 4);
-          } else {
-            x -= pieces_a; kind[i] = 3; src = v + row * A.ldv + j0 + x * VEC;
-            so[i] = t * tok_w + 3 * row_w + x * VEC; so2[i] = so[i] + 4;
-            if (j0 + x * VEC >= dv) src = nullptr;                 // the last tile's columns beyond the head: zeros
-          }
-          r[i] = src ? __ldg(reinterpret_cast<const uint4*>(src)) : make_uint4(0, 0, 0, 0);
+          int t, off;
+          describe(e, t, off, so[i], so2[i], kind[i]);
+          r[i] = fetch(kind[i], off, (size_t)(row0 + t_first + t));
         }
       }
 #pragma unroll
-      for (int i = 0; i < NI; ++i) {
-        if (kind[i] < 0) continue;
-        float* dst = b + so[i];
-        if (kind[i] == 2) { *reinterpret_cast<uint4*>(dst) = r[i]; continue; }
-        float f[VEC];
-        if constexpr (sizeof(T) == 2) {
-          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&r[i]);
+      for (int i = 0; i < NI; ++i) if (kind[i] >= 0) put(b, r[i], so[i], so2[i], kind[i]);
+    }
+  };
+  // the producers' fast form: a chunk is at most NI pieces a producer (A.fast), each described once
+  int p_meta[NI], p_off[NI], p_so[NI], p_so2[NI];          // p_meta: the chunk's row * 8 + kind
+  if (!SINGLE && A.vec && A.fast && producer) {
 #pragma unroll
-          for (int u = 0; u < 4; ++u) { const float2 x2 = __bfloat1622float2(h2[u]); f[2 * u] = x2.x; f[2 * u + 1] = x2.y; }
-        } else {
-          f[0] = __uint_as_float(r[i].x); f[1] = __uint_as_float(r[i].y); f[2] = __uint_as_float(r[i].z); f[3] = __uint_as_float(r[i].w);
-        }
-        if (kind[i] == 0) {
-#pragma unroll
-          for (int u = 0; u < VEC; ++u) f[u] *= A.q_scale;
-        }
-        // groups of four channels never straddle a thread's block of DC (a multiple of four): the padding falls between
-        *reinterpret_cast<float4*>(dst) = make_float4(f[0], f[1], f[2], f[3]);
-        if constexpr (VEC == 8) *reinterpret_cast<float4*>(b + so2[i]) = make_float4(f[4], f[5], f[6], f[7]);
+    for (int i = 0; i < NI; ++i) {
+      const int e = ptid + i * n_prod;
+      p_meta[i] = 1 << 30; p_off[i] = p_so[i] = p_so2[i] = 0;
+      if (e < A.chunk * per_tok_v) {
+        int t, kind;
+        describe(e, t, p_off[i], p_so[i], p_so2[i], kind);
+        p_meta[i] = t * 8 + kind;
       }
     }
+  }
+  auto stage_fast = [&](int ch) {
+    float* b = buf[ch & 1];
+    const int t_first = ch * A.chunk;
+    const int rows = min(A.chunk, n - t_first);
+    const size_t base_row = (size_t)(row0 + t_first);
+    uint4 r[NI];
+#pragma unroll
+    for (int i = 0; i < NI; ++i)
+      if ((p_meta[i] >> 3) < rows) r[i] = fetch(p_meta[i] & 7, p_off[i], base_row + (p_meta[i] >> 3));
+#pragma unroll
+    for (int i = 0; i < NI; ++i) if ((p_meta[i] >> 3) < rows) put(b, r[i], p_so[i], p_so2[i], p_meta[i] & 7);
   };
 
   if (A.vec) {
@@ -258,49 +295,96 @@ gla_scan_kernel(GlaArgs A) {
     stage(0, tid, blockDim.x);
   }
   __syncthreads();
+  const size_t o_ld = (size_t)H * dv;
   for (int ch = 0; ch < n_chunks; ++ch) {
     if (producer) {
-      if (ch + 1 < n_chunks) { if (A.vec) stage_vec(ch + 1, ptid, n_prod); else stage(ch + 1, ptid, n_prod); }
+      if (!SINGLE && ch + 1 < n_chunks) {
+        if (A.vec && A.fast) stage_fast(ch + 1);
+        else if (A.vec) stage_vec(ch + 1, ptid, n_prod);
+        else stage(ch + 1, ptid, n_prod);
+      }
     } else if (owns) {
-      const float* b = buf[ch & 1];
       const int rows = min(A.chunk, n - ch * A.chunk);
-      float* o = A.out + (size_t)(row0 + ch * A.chunk) * ((size_t)H * dv) + (size_t)head * dv + j;
-      // four tokens a turn: the state's chain runs through them one after the other, their sums over the column's
-      // threads meet side by side
-      for (int t0 = 0; t0 < rows; t0 += 4) {
-        float acc[4];
+      const float* r = buf[ch & 1] + l * (DC + 4);
+      const float* rv = buf[ch & 1] + 3 * row_w + (j - j0);
+      float* o = A.out + (size_t)(row0 + ch * A.chunk) * o_ld + (size_t)head * dv + j;
+      int t0 = 0;
+      // Eight tokens a turn.  The state's chain runs through them one after the other; their eight sums over the column's
+      // threads are then formed together: in each round a thread keeps half of its tokens and hands the other half to its
+      // partner (1, 2, 4 lanes away), so that after three rounds every thread holds one token's sum (7 exchanges for 8
+      // tokens instead of 24), which it stores.  Columns of fewer than 8 threads stop earlier and keep several tokens
+      // each; columns of more go on with whole sums.  The order of every sum depends on the sizes alone.
+      for (; !SINGLE && t0 + 8 <= rows; t0 += 8) {
+        float acc[8];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          acc[u] = 0.f;
-          if (t0 + u < rows) {
-            const float* r = b + (size_t)(t0 + u) * tok_w;
-            const float* rq = r + l * (DC + 4);
-            const float* rk = rq + row_w;
-            const float* ra = rk + row_w;
-            const float vj = r[3 * row_w + (j - j0)];
+        for (int u = 0; u < 8; ++u) {
+          const float vj = rv[0];
+          float a0 = 0.f, a1 = 0.f;
 #pragma unroll
-            for (int i = 0; i < DC; i += 4) {
-              const float4 q4 = *reinterpret_cast<const float4*>(rq + i);
-              const float4 k4 = *reinterpret_cast<const float4*>(rk + i);
-              const float4 a4 = *reinterpret_cast<const float4*>(ra + i);
-              s[i] = fmaf(a4.x, s[i], k4.x * vj);             acc[u] = fmaf(q4.x, s[i], acc[u]);
-              s[i + 1] = fmaf(a4.y, s[i + 1], k4.y * vj);     acc[u] = fmaf(q4.y, s[i + 1], acc[u]);
-              s[i + 2] = fmaf(a4.z, s[i + 2], k4.z * vj);     acc[u] = fmaf(q4.z, s[i + 2], acc[u]);
-              s[i + 3] = fmaf(a4.w, s[i + 3], k4.w * vj);     acc[u] = fmaf(q4.w, s[i + 3], acc[u]);
-            }
+          for (int i = 0; i < DC; i += 4) {
+            const float4 q4 = *reinterpret_cast<const float4*>(r + i);
+            const float4 k4 = *reinterpret_cast<const float4*>(r + row_w + i);
+            const float4 a4 = *reinterpret_cast<const float4*>(r + 2 * row_w + i);
+            s[i] = fmaf(a4.x, s[i], k4.x * vj);             a0 = fmaf(q4.x, s[i], a0);
+            s[i + 1] = fmaf(a4.y, s[i + 1], k4.y * vj);     a1 = fmaf(q4.y, s[i + 1], a1);
+            s[i + 2] = fmaf(a4.z, s[i + 2], k4.z * vj);     a0 = fmaf(q4.z, s[i + 2], a0);
+            s[i + 3] = fmaf(a4.w, s[i + 3], k4.w * vj);     a1 = fmaf(q4.w, s[i + 3], a1);
           }
+          acc[u] = a0 + a1;
+          r += tok_w; rv += tok_w;
         }
-        for (int off = L >> 1; off > 0; off >>= 1) {
+        int mine = 0, held = 8;                       // the first token this thread ends up with, and how many
+        if (L > 1) {
+          const bool up = l & 1;
 #pragma unroll
-          for (int u = 0; u < 4; ++u) acc[u] += __shfl_xor_sync(col_mask, acc[u], off);
+          for (int i = 0; i < 4; ++i) {
+            const float give = up ? acc[i] : acc[i + 4], keep = up ? acc[i + 4] : acc[i];
+            acc[i] = keep + __shfl_xor_sync(col_mask, give, 1);
+          }
+          mine += up ? 4 : 0; held = 4;
         }
-        if (l == 0) {
+        if (L > 2) {
+          const bool up = l & 2;
 #pragma unroll
-          for (int u = 0; u < 4; ++u) if (t0 + u < rows) o[(size_t)(t0 + u) * ((size_t)H * dv)] = acc[u];
+          for (int i = 0; i < 2; ++i) {
+            const float give = up ? acc[i] : acc[i + 2], keep = up ? acc[i + 2] : acc[i];
+            acc[i] = keep + __shfl_xor_sync(col_mask, give, 2);
+          }
+          mine += up ? 2 : 0; held = 2;
+        }
+        if (L > 4) {
+          const bool up = l & 4;
+          const float give = up ? acc[0] : acc[1], keep = up ? acc[1] : acc[0];
+          acc[0] = keep + __shfl_xor_sync(col_mask, give, 4);
+          mine += up ? 1 : 0; held = 1;
+        }
+        for (int off = 8; off < L; off <<= 1) acc[0] += __shfl_xor_sync(col_mask, acc[0], off);
+        if (l < 8) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) if (i < held) o[(size_t)(t0 + mine + i) * o_ld] = acc[i];
         }
       }
+      // what is left of the chunk, token by token
+      for (; t0 < rows; ++t0) {
+        const float vj = rv[0];
+        float a0 = 0.f, a1 = 0.f;                 // (the same order of sums as in a turn of eight: the bits do not depend on the cut)
+#pragma unroll
+        for (int i = 0; i < DC; i += 4) {
+          const float4 q4 = *reinterpret_cast<const float4*>(r + i);
+          const float4 k4 = *reinterpret_cast<const float4*>(r + row_w + i);
+          const float4 a4 = *reinterpret_cast<const float4*>(r + 2 * row_w + i);
+          s[i] = fmaf(a4.x, s[i], k4.x * vj);             a0 = fmaf(q4.x, s[i], a0);
+          s[i + 1] = fmaf(a4.y, s[i + 1], k4.y * vj);     a1 = fmaf(q4.y, s[i + 1], a1);
+          s[i + 2] = fmaf(a4.z, s[i + 2], k4.z * vj);     a0 = fmaf(q4.z, s[i + 2], a0);
+          s[i + 3] = fmaf(a4.w, s[i + 3], k4.w * vj);     a1 = fmaf(q4.w, s[i + 3], a1);
+        }
+        float acc1 = a0 + a1;
+        for (int off = 1; off < L; off <<= 1) acc1 += __shfl_xor_sync(col_mask, acc1, off);
+        if (l == 0) o[(size_t)t0 * o_ld] = acc1;
+        r += tok_w; rv += tok_w;
+      }
     }
-    __syncthreads();
+    if (n_chunks > 1) __syncthreads();
   }
   if (owns && A.write_state) {
     if (dk % 4 == 0) {
@@ -320,14 +404,16 @@ template <typename T, int DC>
 static int gla_launch(const GlaArgs& A, int R, cudaStream_t stream, size_t smem) {
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gla_scan_kernel<T, DC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(gla_scan_kernel<T, DC, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gla_scan_kernel<T, DC, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
     if (e != cudaSuccess) QE_REFUSE("linear_attention_scan: shared memory: %s", cudaGetErrorString(e));
     configured = true;
   }
-  const int n_compute = A.VT * A.L;
-  const int threads = ((n_compute + 31) / 32) * 32 + GLA_PRODUCERS;
+  const int n_compute = ((A.VT * A.L + 31) / 32) * 32;
   dim3 grid(R, A.H, (A.dv + A.VT - 1) / A.VT);
-  qe_launch(gla_scan_kernel<T, DC>, grid, dim3(threads), smem, stream, A);
+  // steps of single tokens have one chunk: nobody stages ahead, the CTA is its computing threads alone
+  if (A.chunk == 1) qe_launch(gla_scan_kernel<T, DC, true>, grid, dim3(n_compute), smem, stream, A);
+  else qe_launch(gla_scan_kernel<T, DC, false>, grid, dim3(n_compute + GLA_PRODUCERS), smem, stream, A);
   QE_CHECK_LAUNCH("linear_attention_scan");
   return 0;
 }
@@ -362,11 +448,20 @@ extern "C" int qe_linear_attention_scan(const void* q, const void* k, const void
   A.VT = VT;
   const int row_w = L * DC + ((L * DC) / DC) * 4;
   const int tok_w = 3 * row_w + ((VT + 3) & ~3);
-  int chunk = max_q_len < 16 ? (max_q_len < 1 ? 1 : max_q_len) : 16;
+  // tokens a chunk: up to 24, and for longer prompts few enough that a producer has at most eight pieces of 16 bytes
+  // of a chunk to fetch, which it then describes once for all chunks (measured at 2 048 tokens of 8 heads, 64 key and
+  // 128 value channels: 242 us with chunks of 8, 212 with 16, 206 with 24, 299 with 32, where the pieces are too many;
+  // 128 key channels: 327 us with chunks of 8, 571 with 16)
+  const int vec_n0 = dtype == QE_DTYPE_F32 ? 4 : 8;
+  int chunk_max = 24;
+  while (chunk_max > 8 && chunk_max * (2 * (dk / vec_n0) + dk / 4 + VT / vec_n0) > 8 * GLA_PRODUCERS) chunk_max -= 8;
+  int chunk = max_q_len < chunk_max ? (max_q_len < 1 ? 1 : max_q_len) : chunk_max;
   while (chunk > 1 && (size_t)2 * chunk * tok_w * sizeof(float) > 96 * 1024) chunk >>= 1;
   A.chunk = chunk;
   // pieces of 16 bytes: whole pieces per head and per tile of value channels, rows and bases on 16-byte boundaries
   const int vec_n = dtype == QE_DTYPE_F32 ? 4 : 8;
+  const int per_tok_pieces = 2 * (dk / vec_n) + dk / 4 + VT / vec_n;
+  A.fast = chunk * per_tok_pieces <= 8 * GLA_PRODUCERS;
   A.vec = dk % vec_n == 0 && dk % 4 == 0 && VT % vec_n == 0 && dv % vec_n == 0 && ldq % vec_n == 0 && ldk % vec_n == 0 &&
           ldv % vec_n == 0 && (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)alpha) & 15) == 0;
   const size_t smem = (size_t)2 * chunk * tok_w * sizeof(float);

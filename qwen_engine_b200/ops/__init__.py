@@ -63,6 +63,9 @@ TC_PART_COST_STEPS = 5.0      # a part's scratch or merge on top, in key steps (
 TC_FORCE_CAP = -1       # the most key steps of a work item (0: cut nothing); below 0 the library works it out
 
 
+GATE_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}     # the functions a gated feed-forward may put on its gate
+
+
 class ExtensionMissing(RuntimeError):
     """The CUDA extension could not be built or loaded."""
 
@@ -479,9 +482,9 @@ def swiglu_fused_applies(M: int, I: int, K: int, dtype: torch.dtype) -> bool:
             and M > SMALL_M_MAX and -(-M // 256) * -(-I // 128) >= PAIR_MIN_TILES)
 
 
-def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[M, I] = silu(x · w[:I]^T) * (x · w[I:]^T) for the stacked weights w [2 I, K]: the feed-forward's
-    activation formed in the product's epilogue on its float32 sums (bfloat16, many rows)."""
+def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> None:
+    """out[M, I] = act(x · w[:I]^T) * (x · w[I:]^T) for the stacked weights w [2 I, K]: the feed-forward's
+    activation (``GATE_ACTIVATIONS``) formed in the product's epilogue on its float32 sums (bfloat16, many rows)."""
     M, K = x.shape
     I = w_gate_up.shape[0] // 2
     _need(x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and w_gate_up.shape == (2 * I, K) and K % 8 == 0,
@@ -489,7 +492,7 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -
     _need(out.shape == (M, I) and out.dtype in (torch.bfloat16, torch.float32), "linear_swiglu: out must be [M, I]")
     _need(x.is_contiguous() and w_gate_up.is_contiguous() and out.is_contiguous(), "linear_swiglu: operands must be contiguous")
     _check(lib().qe_linear_swiglu_tcgen05_pair(_ptr(x), _ptr(w_gate_up), _ptr(out), M, I, K,
-                                               int(out.dtype == torch.float32), _stream()), "linear_swiglu")
+                                               int(out.dtype == torch.float32), GATE_ACTIVATIONS[activation], _stream()), "linear_swiglu")
 
 
 SWIGLU_SMALL_MAX_M = 16     # rows up to which the weight-streaming product forms the activation in its epilogue
@@ -500,8 +503,8 @@ def swiglu_small_applies(M: int, I: int, K: int, dtype: torch.dtype) -> bool:
     return dtype == torch.bfloat16 and 1 <= M <= SWIGLU_SMALL_MAX_M and K % 8 == 0
 
 
-def linear_swiglu_small(x, w_gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[M, I] = silu(x · w[:I]^T) * (x · w[I:]^T) for the stacked weights w [2 I, K] and a few rows (decode steps):
+def linear_swiglu_small(x, w_gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> None:
+    """out[M, I] = act(x · w[:I]^T) * (x · w[I:]^T) for the stacked weights w [2 I, K] and a few rows (decode steps):
     a CTA streams the gate rows and the up rows of the same 16 columns and forms the activation in its epilogue, so
     that gate and up never exist in memory and the product that follows reads half the bytes, already activated."""
     if isinstance(x, NormedInput):
@@ -514,7 +517,8 @@ def linear_swiglu_small(x, w_gate_up: torch.Tensor, out: torch.Tensor) -> None:
           f"linear_swiglu_small: out must be bfloat16 [M, I] with M <= {SWIGLU_SMALL_MAX_M}")
     _need(x.is_contiguous() and w_gate_up.is_contiguous() and out.is_contiguous(), "linear_swiglu_small: operands must be contiguous")
     _hand_over_next_weights()
-    _check(lib().qe_linear_small_m_swiglu(_ptr(x), _ptr(w_gate_up), _ptr(out), M, I, K, _stream()), "linear_swiglu_small")
+    _check(lib().qe_linear_small_m_swiglu(_ptr(x), _ptr(w_gate_up), _ptr(out), M, I, K, GATE_ACTIVATIONS[activation], _stream()),
+           "linear_swiglu_small")
 
 
 QKV_ROPE_FUSED = True       # many rows: per-head norm, rotation and cache write in the epilogue of the QKV product
@@ -1148,9 +1152,6 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
     _need(I2 % 2 == 0 and out.shape == (T, I2 // 2) and out.dtype == gate_up.dtype
           and out.is_contiguous() and gate_up.is_contiguous(), "silu_mul: out must be [T, I] for gate_up [T, 2I]")
     _check(lib().qe_silu_mul(_ptr(gate_up), _ptr(out), T, I2 // 2, _dt(out), _stream()), "silu_mul")
-
-
-GATE_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
 
 
 def act_mul(gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> None:

@@ -5,9 +5,10 @@ over the stacked weights.
 
 The same part serves other gated feed-forwards: ``activation`` names the
 function on the gate ("silu", or "gelu_tanh": 0.5 z (1 + tanh(sqrt(2/pi) (z +
-0.044715 z^3)))), ``names`` the three tensors.  The products that form SiLU-mul
-in their own epilogue are asked for "silu" only; another activation runs as
-product, activation kernel, product."""
+0.044715 z^3)))), ``names`` the three tensors.  The gate/up products that form
+the activation in their own epilogue take either; the down product that forms
+SiLU-mul while it loads (some tens of rows) is SiLU's alone, so another
+activation runs there as product, activation kernel, product."""
 from __future__ import annotations
 
 import torch
@@ -49,29 +50,19 @@ class SwiGLU(FeedForward):
 
     def forward(self, ctx: StepContext, x, out) -> None:
         T, I = ctx.num_tokens, self.intermediate_size
-        if self.activation != "silu":
-            gate_up = ctx.arena.alloc((T, 2 * I), ctx.dtype)
-            act = ctx.arena.alloc((T, I), ctx.dtype)
-            ops.prefetch_next(self.w_down)
-            ops.linear(x, self.w_gate_up, gate_up)
-            ops.act_mul(gate_up, act, self.activation)
-            ops.prefetch_next(step_hint(ctx, "weights_after_ffn"))
-            ops.linear(act, self.w_down, out)
-            ops.prefetch_next(None)
-            return
         if ops.swiglu_fused_applies(T, I, self.hidden_size, ctx.dtype):
             # many rows: the activation comes out of the gate/up product's epilogue
             if isinstance(x, ops.NormedInput):
                 x = x.materialize()
             act = ctx.arena.alloc((T, I), ctx.dtype)
-            ops.linear_swiglu(x, self.w_gate_up, act)
+            ops.linear_swiglu(x, self.w_gate_up, act, self.activation)
             ops.linear(act, self.w_down, out)
             return
         if ops.swiglu_small_applies(T, I, self.hidden_size, ctx.dtype):
             # a few rows: the product that streams the gate and up weights forms the activation itself
             act = ctx.arena.alloc((T, I), ctx.dtype)
             ops.prefetch_next(self.w_down)
-            ops.linear_swiglu_small(x, self.w_gate_up, act)
+            ops.linear_swiglu_small(x, self.w_gate_up, act, self.activation)
             ops.prefetch_next(step_hint(ctx, "weights_after_ffn"))
             ops.linear(act, self.w_down, out)
             ops.prefetch_next(None)
@@ -80,5 +71,10 @@ class SwiGLU(FeedForward):
         ops.prefetch_next(self.w_down)
         ops.linear(x, self.w_gate_up, gate_up)
         ops.prefetch_next(step_hint(ctx, "weights_after_ffn"))
-        ops.linear_silu_mul(gate_up, self.w_down, out, ctx.arena.alloc)
+        if self.activation == "silu":
+            ops.linear_silu_mul(gate_up, self.w_down, out, ctx.arena.alloc)
+        else:
+            act = ctx.arena.alloc((T, I), ctx.dtype)
+            ops.act_mul(gate_up, act, self.activation)
+            ops.linear(act, self.w_down, out)
         ops.prefetch_next(None)

@@ -191,6 +191,23 @@ def test_gelu_mul_and_scaled_embedding(ops, dtype):
     _close(stream, 2 * want, F32, "embedding added again", tol=1e-6)
 
 
+@pytest.mark.parametrize("M,I,K", [(3, 96, 64), (16, 3072, 1024), (1200, 3072, 512), (2048, 3072, 1024)])
+def test_gate_up_product_with_gelu_in_its_epilogue(ops, M, I, K):
+    """The two products that form act(gate) * up themselves (a few rows; many rows), with the tanh form of gelu."""
+    g = torch.Generator().manual_seed(M + I)
+    x = torch.randn(M, K, generator=g).to(BF16)
+    w = (torch.randn(2 * I, K, generator=g) * (2.0 / math.sqrt(K))).to(BF16)
+    out = torch.empty(M, I, dtype=BF16, device=DEV)
+    if M <= 16:
+        assert ops.swiglu_small_applies(M, I, K, BF16)
+        ops.linear_swiglu_small(x.to(DEV), w.to(DEV), out, "gelu_tanh")
+    else:
+        assert ops.swiglu_fused_applies(M, I, K, BF16)
+        ops.linear_swiglu(x.to(DEV), w.to(DEV), out, "gelu_tanh")
+    gate, up = x.double() @ w[:I].double().T, x.double() @ w[I:].double().T
+    _close(out, plain.gelu_tanh(gate) * up, BF16, "gelu in the epilogue")
+
+
 # ---- windowed attention with a distance bias ------------------------------------------------------------------------------
 def _attention_case(Hq, Hkv, D, P, q_lens, ctx_lens, dtype, seed, spikes=()):
     g = torch.Generator().manual_seed(seed)
