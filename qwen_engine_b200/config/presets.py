@@ -42,12 +42,26 @@ PRESETS: dict[str, dict[str, Any]] = {
         config=dict(_QWEN3_COMMON, num_hidden_layers=36, hidden_size=2560,
                     num_attention_heads=32, num_key_value_heads=8, intermediate_size=9728),
         init=dict(seed=4, std=0.02, norm_std=0.1, block_size=16)),
+    # a small model of the Ganidra design: gated linear attention, and windowed softmax attention beside it, the
+    # first two layers passed twice
+    "ganidra-tiny": dict(
+        config=dict(architecture="Ganidra", vocab=320, width=128, embedding=dict(scale=2.0), norm=dict(eps=1e-6),
+                    layers=[dict(type="gla", mixer=dict(heads=4, dim=16, vdim=32, tau=8.0, rank=8), mlp=None),
+                            dict(type="parallel",
+                                 mixer=dict(left=dict(heads=4, kv_heads=2, dim=32, vdim=32, mask=dict(size=48), scale=0.17),
+                                            right=dict(heads=2, dim=16, vdim=32, tau=8.0, rank=8),
+                                            left_scale=0.7, right_scale=0.7),
+                                 mlp=dict(kind="dense", ff=256)),
+                            dict(type="gla", mixer=dict(heads=4, dim=16, vdim=32, tau=4.0, rank=8), mlp=dict(kind="dense", ff=192))],
+                    loop=dict(start=0, stop=2, times=2)),
+        init=dict(seed=5, std=0.08, norm_std=0.1, block_size=16)),
 }
 
 
 def preset_config_dict(name: str) -> dict[str, Any]:
     try:
-        return dict(PRESETS[name]["config"])
+        import copy
+        return copy.deepcopy(dict(PRESETS[name]["config"]))
     except KeyError:
         raise ValueError(f"unknown preset {name!r}; known: {sorted(PRESETS)}") from None
 
