@@ -198,6 +198,9 @@ decode_attention_mma_kernel(FaArgs A, long long prefetch_delta, int early_issue,
   // ---- this warp's groups ---------------------------------------------------------------------------------
   const int g = lane >> 2;
   const int pos_lo = first_pos + g / G, pos_hi = first_pos + (g + 8) / G;
+  const bool biased = A.slopes != nullptr;
+  const float slope_lo = biased ? A.slopes[hkv * G + g % G] * 1.4426950408889634f : 0.f;
+  const float slope_hi = biased ? A.slopes[hkv * G + (g + 8) % G] * 1.4426950408889634f : 0.f;
   const int last_pos = first_pos + ntok - 1;
   float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
   float o[D / 8][4];
@@ -212,8 +215,12 @@ decode_attention_mma_kernel(FaArgs A, long long prefetch_delta, int early_issue,
     const __nv_bfloat16* tk = reinterpret_cast<const __nv_bfloat16*>(my_stages + (size_t)st * 2 * DM_TILE_BYTES);
     const __nv_bfloat16* tv = tk + DM_GK * LD;
     const bool all_allowed = j0 + DM_GK <= kv_end && j0 + DM_GK - 1 <= first_pos && (window <= 0 || j0 > last_pos - window);
-    fa_tile<D, 1>(sq, tk, tv, 0, 0, j0, kv_begin, kv_end, pos_lo, pos_hi, window, A.scale_log2, lane,
-                  m_lo, m_hi, l_lo, l_hi, o, all_allowed);
+    if (biased)         // a distance bias on the scores (the slopes of the rows' heads, in units of log2 e)
+      fa_tile<D, 1, true>(sq, tk, tv, 0, 0, j0, kv_begin, kv_end, pos_lo, pos_hi, window, A.scale_log2, lane,
+                          m_lo, m_hi, l_lo, l_hi, o, all_allowed, slope_lo, slope_hi);
+    else
+      fa_tile<D, 1>(sq, tk, tv, 0, 0, j0, kv_begin, kv_end, pos_lo, pos_hi, window, A.scale_log2, lane,
+                    m_lo, m_hi, l_lo, l_hi, o, all_allowed);
     __syncwarp();                                   // every lane is done with the stage before it is filled again
     const int nxt = gidx + DM_STAGES * DM_WARPS;
     if (nxt < n_groups) issue(nxt, st);
@@ -460,7 +467,7 @@ extern "C" int qe_decode_attention_mma_supported(int Hq, int Hkv, int D, int max
 extern "C" int qe_decode_attention_mma(const void* q, long q_stride, const void* pages, const void* prefetch_pages, const int* block_tables,
                                        int max_blocks, const int* items, int n_items, void* out, float* part_acc,
                                        float* part_ml, int part_rows, int* counters, int max_rows, int cluster, int wide, float scale,
-                                       int window, int Hq, int Hkv, int D, int page_size, cudaStream_t stream) {
+                                       int window, int Hq, int Hkv, int D, int page_size, const float* slopes, cudaStream_t stream) {
   if (n_items <= 0) return 0;
   if (!qe_decode_attention_mma_supported(Hq, Hkv, D, max_rows))
     QE_REFUSE("decode_attention_mma: heads %d/%d, head_dim %d, %d rows are not supported", Hq, Hkv, D, max_rows);
@@ -470,7 +477,7 @@ extern "C" int qe_decode_attention_mma(const void* q, long q_stride, const void*
   if (part_acc && counters == nullptr && !cluster) QE_REFUSE("decode_attention_mma: parts need the counters");
   FaArgs fa{(const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)pages, block_tables, max_blocks, items,
             (__nv_bfloat16*)out, part_acc, part_ml, part_rows, counters, scale * 1.4426950408889634f, window, Hq, Hkv,
-            page_size};
+            page_size, slopes};
   if (cluster == 0) return launch_decode_mma<false>(fa, delta, n_items, Hkv, 0, wide, max_rows, stream);
   if ((cluster != 2 && cluster != 4 && cluster != 8) || n_items % cluster)
     QE_REFUSE("decode_attention_mma: %d items cannot form clusters of %d", n_items, cluster);

@@ -76,6 +76,7 @@ struct AtArgs {
   const int* items; const int* sched; __nv_bfloat16* out;
   float* part_acc; float* part_ml; int part_rows; int* counters;
   float scale_log2; int window, Hq, Hkv, page_shift;
+  const float* slopes; float inv_scale;     // null, or float32 [Hq]: slopes[h] (position - key) is taken off the score
 };
 
 __device__ __forceinline__ uint32_t at_pack(float lo, float hi) {
@@ -425,6 +426,9 @@ flash_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
       const int pos = valid ? U.first_pos + r / G : -1;
       const int hi = valid ? min(U.kv_end, pos + 1) : 0;      // keys [lo, hi) are allowed for this row
       const int lo = window > 0 ? max(U.kv_begin, pos - window + 1) : U.kv_begin;
+      // a distance bias: slope (key - position) joins the raw score as slope / scale times the distance, so that
+      // the maxima, the scale and the exponentials below see it like any score (row r is head hkv G + r % G)
+      const float kb = A.slopes ? A.slopes[hkv * G + r % G] * A.inv_scale : 0.f;
       float m_run = -INFINITY, l_run = 0.f;
       // (timeline build: 0 the unit's first scores are ready, 1 its first P is handed over, 2 its last P, 3 its last P V has
       // retired, 4 its output is written, 5 the parts are merged, if that fell to this CTA)
@@ -441,6 +445,14 @@ flash_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
           for (int c = 0; c < 4; ++c) tc_ld_32x32b_x32(lane_base + s_col + c * 32, s[c]);
           tc_wait_ld();
           const int kt = U.kt_first + j * AT_BN;
+          if (A.slopes) {                                 // (the kernel's, not the row's: no lane idles)
+            const float b0 = kb * (float)(kt - pos);
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                s[c][i] = __float_as_uint(__uint_as_float(s[c][i]) + fmaf(kb, (float)(32 * c + i), b0));
+          }
           float mx = -INFINITY;
           // A step's 128 keys as four runs of 32: where a run is allowed for all of the warp's rows (every run of a step
           // before the diagonal) the maxima are chains of three-input instructions; where it is forbidden for all of
@@ -895,7 +907,7 @@ extern "C" int qe_flash_attention_tc(const void* q, long q_stride, int T, const 
                                      const int* sched, int n_ctas,
                                      void* out, float* part_acc, float* part_ml, int part_rows, int* counters,
                                      float scale, int window, int Hq, int Hkv, int D, int page_size,
-                                     cudaStream_t stream) {
+                                     const float* slopes, cudaStream_t stream) {
   if (n_items <= 0) return 0;
   if (sched == nullptr || n_ctas <= 0 || (long)n_ctas > (long)n_items * Hkv)
     QE_REFUSE("flash_attention_tc: a schedule for 1 to %ld CTAs is needed, not one for %d", (long)n_items * Hkv, n_ctas);
@@ -924,7 +936,7 @@ extern "C" int qe_flash_attention_tc(const void* q, long q_stride, int T, const 
   int page_shift = 0;
   while ((1 << page_shift) < page_size) ++page_shift;
   AtArgs args{block_tables, max_blocks, num_pages, items, sched, (__nv_bfloat16*)out, part_acc, part_ml, part_rows, counters,
-              scale * 1.4426950408889634f, window, Hq, Hkv, page_shift};
+              scale * 1.4426950408889634f, window, Hq, Hkv, page_shift, slopes, 1.f / scale};
   const size_t smem = sizeof(AtSmem) + 1024;
   static bool configured = false;
   if (!configured) {

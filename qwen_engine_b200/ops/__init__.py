@@ -922,7 +922,7 @@ def plan_attention(q_lens: list[int], ctx_lens: list[int], page_size: int,
             continue
         G = Hq // Hkv
         tpt = FLASH_ROWS // G
-        use_tc = uniform_splits is None and not biased and tc_attention_supported(dtype, Hq, Hkv, D, page_size)
+        use_tc = uniform_splits is None and tc_attention_supported(dtype, Hq, Hkv, D, page_size)
         on_tc = [use_tc and n * G >= TC_MIN_ROWS for n in q_lens]
         tc_tiles: list = []
         base = sum(-(-n // tpt) for n, tc in zip(q_lens, on_tc) if not tc) * Hkv
@@ -1062,7 +1062,6 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
     index = plan.get("geometry_index", {})
     key = index.get((Hq, Hkv, D, window, True)) if slopes is not None else index.get((Hq, Hkv, D, window), index.get((Hq, Hkv, D, window, False)))
     if key is not None and f"tc{key}_items" in plan:
-        _need(slopes is None, "paged_attention: the tcgen05 kernel takes no distance bias")
         last_attention_kernel = "flash_attention_tc"
         tc_items = plan[f"tc{key}_items"]
         tc_parts, tc_rows, tc_ctas = plan[f"tc{key}_info_host"]
@@ -1077,7 +1076,7 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
             int(block_tables.shape[1]), _ptr(tc_items), tc_items.numel() // FLASH_ITEM_INTS,
             _ptr(plan[f"tc{key}_sched"]), int(tc_ctas), _ptr(out),
             _ptr(part_acc), _ptr(part_ml), int(tc_rows), _ptr(counters), ctypes.c_float(scale), int(window),
-            Hq, Hkv, D, int(kv_pages.shape[3]), _stream()), "flash_attention_tc")
+            Hq, Hkv, D, int(kv_pages.shape[3]), _ptr(slopes), _stream()), "flash_attention_tc")
     if key is not None and f"fa{key}_items" in plan:
         items, merge = plan[f"fa{key}_items"], plan[f"fa{key}_merge"]
         n_parts, part_rows, small_tiles, max_rows, same_parts = plan[f"fa{key}_info_host"]
@@ -1091,7 +1090,7 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
         counters = _merge_counters(qkv.device) if 0 < n_parts * Hkv <= _MERGE_COUNTERS else None
         # every request in the same few parts: the parts of a request form a cluster and meet on chip
         cluster = int(same_parts) if DECODE_ATTENTION_CLUSTERS and n_items == n_parts else 0
-        if slopes is None and _decode_mma_serves(plan, key, qkv, Hq, Hkv, D):
+        if _decode_mma_serves(plan, key, qkv, Hq, Hkv, D):
             # decoded tokens: every warp streams key groups of its own through the tensor cores
             last_attention_kernel = "decode_attention_mma"
             lib().qe_decode_attention_mma_stages(int(DECODE_ATTENTION_MMA_STAGES))
@@ -1106,7 +1105,7 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
                 _ptr(qkv), ctypes.c_long(qkv.stride(0)), _ptr(kv_pages), _ptr(ahead), _ptr(block_tables), int(block_tables.shape[1]),
                 _ptr(items), n_items, _ptr(out), _ptr(part_acc), _ptr(part_ml), int(part_rows), _ptr(counters),
                 int(max_rows), cluster, int(DECODE_ATTENTION_MMA_WIDE and n_items * Hkv <= TC_TARGET_CTAS),
-                ctypes.c_float(scale), int(window), Hq, Hkv, D, int(kv_pages.shape[3]), _stream()),
+                ctypes.c_float(scale), int(window), Hq, Hkv, D, int(kv_pages.shape[3]), _ptr(slopes), _stream()),
                 "decode_attention_mma")
             return
         last_attention_kernel = "flash_attention"

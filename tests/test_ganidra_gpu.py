@@ -276,9 +276,26 @@ def test_attention_with_window_and_distance_bias(ops, dtype, flash, Hq, Hkv, D, 
     qkv, cache, table = _attention_case(Hq, Hkv, D, P, q_lens, ctx_lens, dtype, Hq * D + len(q_lens))
     scale = 0.9 / math.sqrt(D)
     got, kernel = _run_attention(ops, qkv, cache, table, Hq, Hkv, D, P, q_lens, ctx_lens, scale, slopes, window, dtype, flash)
-    assert kernel == ("flash_attention" if flash else "paged_attention_generic")
+    assert kernel in (("flash_attention", "flash_attention_tc", "decode_attention_mma") if flash else ("paged_attention_generic",))
     want = _plain_attention(qkv, cache, table, Hq, Hkv, D, P, q_lens, ctx_lens, scale, slopes, window)
     _close(got, want, dtype, kernel, tol={F32: 2e-5, BF16: 2e-2}[dtype])
+
+
+@pytest.mark.parametrize("q_lens,ctx_lens,kernel", [([300], [0], "flash_attention_tc"), ([130], [77], "flash_attention_tc"),
+                                                    ([1, 1, 1, 1], [300, 17, 512, 64], "decode_attention_mma"),
+                                                    ([2, 1], [200, 90], "decode_attention_mma")])
+@pytest.mark.parametrize("window", [64, 200])
+def test_biased_attention_on_the_kernels_of_head_size_128(ops, q_lens, ctx_lens, kernel, window):
+    """Head size 128: prompt portions on the tcgen05 kernel, decoded tokens on the warp-pipelined kernel, both with
+    the distance bias and a window that ends inside their key steps."""
+    Hq, Hkv, D, P = 8, 2, 128, 16
+    slopes = [2.0 ** (-8.0 * (h + 1) / Hq) for h in range(Hq)]
+    qkv, cache, table = _attention_case(Hq, Hkv, D, P, q_lens, ctx_lens, BF16, 5 + len(q_lens))
+    scale = 1.0 / math.sqrt(D)
+    got, used = _run_attention(ops, qkv, cache, table, Hq, Hkv, D, P, q_lens, ctx_lens, scale, slopes, window, BF16, True)
+    assert used == kernel
+    want = _plain_attention(qkv, cache, table, Hq, Hkv, D, P, q_lens, ctx_lens, scale, slopes, window)
+    _close(got, want, BF16, kernel, tol=2e-2)
 
 
 @pytest.mark.parametrize("dtype,flash", [(F32, False), (BF16, True)])
