@@ -99,6 +99,7 @@ struct GlaArgs {
   float q_scale;
   int H, dk, dv, L, VT, chunk, write_state;
   int vec;                                            // q, k, v, alpha can be staged in pieces of 16 bytes
+  int single;                                         // every request brings one token
   int fast;                                           // ... and a chunk is at most 8 pieces a producer
 };
 
@@ -412,7 +413,7 @@ static int gla_launch(const GlaArgs& A, int R, cudaStream_t stream, size_t smem)
   const int n_compute = ((A.VT * A.L + 31) / 32) * 32;
   dim3 grid(R, A.H, (A.dv + A.VT - 1) / A.VT);
   // steps of single tokens have one chunk: nobody stages ahead, the CTA is its computing threads alone
-  if (A.chunk == 1) qe_launch(gla_scan_kernel<T, DC, true>, grid, dim3(n_compute), smem, stream, A);
+  if (A.single) qe_launch(gla_scan_kernel<T, DC, true>, grid, dim3(n_compute), smem, stream, A);
   else qe_launch(gla_scan_kernel<T, DC, false>, grid, dim3(n_compute + GLA_PRODUCERS), smem, stream, A);
   QE_CHECK_LAUNCH("linear_attention_scan");
   return 0;
@@ -458,6 +459,7 @@ extern "C" int qe_linear_attention_scan(const void* q, const void* k, const void
   int chunk = max_q_len < chunk_max ? (max_q_len < 1 ? 1 : max_q_len) : chunk_max;
   while (chunk > 1 && (size_t)2 * chunk * tok_w * sizeof(float) > 96 * 1024) chunk >>= 1;
   A.chunk = chunk;
+  A.single = max_q_len <= 1;      // (a chunk of one token can also be all that fits shared memory: that is not this case)
   // pieces of 16 bytes: whole pieces per head and per tile of value channels, rows and bases on 16-byte boundaries
   const int vec_n = dtype == QE_DTYPE_F32 ? 4 : 8;
   const int per_tok_pieces = 2 * (dk / vec_n) + dk / 4 + VT / vec_n;

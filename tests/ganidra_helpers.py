@@ -55,6 +55,18 @@ GANIDRA = {
                                                          left_scale=0.8, right_scale=0.8), ff=384)],
                          loop=dict(start=0, stop=2, times=2)),
                 seed=13, std=0.05, norm_std=0.1, page=16),
+    # a middle size: five layers, the second and third passed twice, a window longer than several pages and one shorter
+    # than two, grouped heads, keys smaller than values
+    "g-e": dict(cfg=dict(architecture="Ganidra", vocab=1000, width=384, embedding=dict(scale=8.0), norm=dict(eps=1e-6),
+                         layers=[_layer("gla", _gla(6, 32, 64, 16.0, 16)),
+                                 _layer("parallel", dict(left=_soft(6, 2, 64, 64, 100, 0.125), right=_gla(3, 32, 32, 8.0, 8),
+                                                         left_scale=0.6, right_scale=0.9), ff=768),
+                                 _layer("gla", _gla(4, 48, 96, 12.0, 12), ff=512),
+                                 _layer("parallel", dict(left=_soft(4, 4, 48, 80, 31, 0.15), right=_gla(6, 16, 32, 2.0, 4),
+                                                         left_scale=1.0, right_scale=1.0)),
+                                 _layer("gla", _gla(6, 32, 64, 16.0, 16))],
+                         loop=dict(start=1, stop=3, times=2)),
+                seed=21, std=0.04, norm_std=0.1, page=16),
 }
 
 

@@ -86,7 +86,7 @@ def _plain_scan(wide, alpha, H, dk, dv, q_scale, rows):
                       for h in range(H)], dim=1)
 
 
-SCAN_SHAPES = [(1, 10, 7), (2, 16, 24), (3, 128, 128), (1, 256, 64), (2, 64, 200), (5, 4, 4), (1, 48, 96)]
+SCAN_SHAPES = [(1, 10, 7), (2, 16, 24), (3, 128, 128), (1, 256, 64), (2, 64, 200), (5, 4, 4), (1, 48, 96), (1, 512, 8), (1, 1024, 4)]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -343,6 +343,30 @@ def test_every_position_of_a_long_prompt_whole_and_decoded(folders, dtype):
         rep = gh.make_replayer(folder, name, dtype, 384)
         gh.check_requests(run_steps(rep, single), folder, {"a": toks}, dtype, f"{name} decoded")
         assert rep.runner.num_graph_replays > n // 2
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_long_prompt_in_portions_then_decoded_at_a_middle_size(folders, dtype):
+    """600 tokens: whole; and in portions of changing sizes (two tokens among them, cuts inside pages and windows)
+    with the last 40 tokens one by one, beside a second request that comes and goes (its slot and pages are used again)."""
+    name = "g-e"
+    folder = folders[name]
+    V = gh.vocab_of(name)
+    toks, other = random_tokens(V, 600, 3), random_tokens(V, 50, 4)
+    want = sorted(set(range(0, 600, 7)) | set(range(560, 600)))
+    whole = [{"entries": [{"id": "a", "tokens": toks, "want": want}], "end": ["a"]}]
+    gh.check_requests(run_steps(gh.make_replayer(folder, name, dtype, 640), whole), folder, {"a": toks}, dtype, "whole")
+    steps, p = [], 0
+    for i, n in enumerate([64, 64, 100, 2, 30, 129, 16, 3, 95, 57] + [1] * 40):
+        entries = [{"id": "a", "tokens": toks[p:p + n], "want": [w - p for w in want if p <= w < p + n]}]
+        if i in (1, 5, 12):                        # a short request beside it, three times over: admitted, run, ended
+            entries.append({"id": f"b{i}", "tokens": other, "want": [49]})
+        steps.append({"entries": entries, "end": [f"b{i}"] if i in (1, 5, 12) else []})
+        p += n
+    assert p == 600
+    rep = gh.make_replayer(folder, name, dtype, 704)
+    got = run_steps(rep, steps)
+    gh.check_requests(got, folder, {"a": toks, "b1": other, "b5": other, "b12": other}, dtype, "portions")
 
 
 def test_greedy_generation_through_the_engine(folders):
