@@ -100,6 +100,8 @@ struct GlaArgs {
   int H, dk, dv, L, VT, chunk, write_state;
   int vec;                                            // q, k, v, alpha can be staged in pieces of 16 bytes
   int single;                                         // every request brings one token
+  // single tokens may bring the decay's inputs instead of alpha: alpha = exp(logsigmoid(a . w[c] + bias[c]) / tau)
+  const void* da; long lda; const void* dw; const float* dbias; float inv_tau; int R;
   int fast;                                           // ... and a chunk is at most 8 pieces a producer
 };
 
@@ -170,6 +172,7 @@ gla_scan_kernel(GlaArgs A) {
       float* dst = b + (size_t)t * tok_w;
       if (x < 3 * padded) {
         const int which = x / padded, c = x - which * padded;
+        if (which == 2 && c < dk && A.alpha == nullptr) continue;      // the kernel forms this decay itself, below
         float val;
         if (c >= dk) val = which == 2 ? 1.f : 0.f;                     // channels beyond the head: nothing in, nothing out
         else if (which == 0) val = to_f32(q[row * A.ldq + c]) * A.q_scale;
@@ -214,13 +217,13 @@ gla_scan_kernel(GlaArgs A) {
     }
   };
   auto fetch = [&](int kind, int off, size_t row) -> uint4 {
-    if (kind > 3) return make_uint4(0, 0, 0, 0);
+    if (kind > 3 || (kind == 2 && A.alpha == nullptr)) return make_uint4(0, 0, 0, 0);
     const char* base = kind == 0 ? base_of[0] : kind == 1 ? base_of[1] : kind == 2 ? base_of[2] : base_of[3];
     const long rb = kind == 0 ? row_bytes_of[0] : kind == 1 ? row_bytes_of[1] : kind == 2 ? row_bytes_of[2] : row_bytes_of[3];
     return __ldg(reinterpret_cast<const uint4*>(base + row * rb + off));
   };
   auto put = [&](float* b, const uint4& r, int so, int so2, int kind) {
-    if (kind == 2) { *reinterpret_cast<uint4*>(b + so) = r; return; }      // (kinds 3 and 4 are values: no scale)
+    if (kind == 2) { if (A.alpha) *reinterpret_cast<uint4*>(b + so) = r; return; }      // (absent: the kernel forms the decay itself)
     float f[VEC];
     if constexpr (sizeof(T) == 2) {
       const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&r);
@@ -294,6 +297,18 @@ gla_scan_kernel(GlaArgs A) {
     stage_vec(0, tid, blockDim.x);
   } else {
     stage(0, tid, blockDim.x);
+  }
+  if (SINGLE && A.da) {
+    // the request's one token: the decay of this head's channels from the low-rank pair's second half, in the order
+    // of sums of the kernel that does this for many tokens (the same bits)
+    const T* a = (const T*)A.da + (size_t)row0 * A.lda;
+    for (int c = tid; c < dk; c += blockDim.x) {
+      const T* wr = (const T*)A.dw + ((size_t)head * dk + c) * A.R;
+      float z = A.dbias ? A.dbias[head * dk + c] : 0.f;
+      for (int r = 0; r < A.R; ++r) z = fmaf(to_f32(a[r]), to_f32(wr[r]), z);
+      const float logsig = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
+      smem[2 * row_w + gla_pad<DC>(c)] = expf(logsig * A.inv_tau);
+    }
   }
   __syncthreads();
   const size_t o_ld = (size_t)H * dv;
@@ -427,11 +442,17 @@ static void gla_shape(int dk, int* DC, int* L) {
   *DC = dc; *L = l;
 }
 
+// alpha null (steps of single tokens only): the decay comes from decay_a [T, rank] (rows of lda elements), decay_w
+// [H dk, rank] in the type of q, decay_bias float32 [H dk] and tau, as qe_channel_decay computes it.
 extern "C" int qe_linear_attention_scan(const void* q, const void* k, const void* v, long ldq, long ldk, long ldv,
                                         const float* alpha, float* state, const int* cu_q, const int* ctx_lens,
                                         const int* slot_ids, float* out, float q_scale, int R, int max_q_len, int H,
-                                        int dk, int dv, int write_state, int dtype, cudaStream_t stream) {
+                                        int dk, int dv, int write_state, int dtype, const void* decay_a, long lda,
+                                        const void* decay_w, const float* decay_bias, float tau, int rank,
+                                        cudaStream_t stream) {
   if (R <= 0) return 0;
+  if (alpha == nullptr && (decay_a == nullptr || decay_w == nullptr || rank < 1 || !(tau > 0.f) || max_q_len > 1))
+    QE_REFUSE("linear_attention_scan: without alpha, a step of single tokens must bring the decay's inputs");
   if (dk < 1 || dk > 1024 || dv < 1) QE_REFUSE("linear_attention_scan: key size %d must be 1..1024, value size %d positive", dk, dv);
   if (H < 1 || H > 65535) QE_REFUSE("linear_attention_scan: %d heads", H);
   int DC, L;
@@ -441,6 +462,7 @@ extern "C" int qe_linear_attention_scan(const void* q, const void* k, const void
   A.q = q; A.k = k; A.v = v; A.ldq = ldq; A.ldk = ldk; A.ldv = ldv; A.alpha = alpha; A.state = state;
   A.cu_q = cu_q; A.ctx_lens = ctx_lens; A.slot_ids = slot_ids; A.out = out; A.q_scale = q_scale;
   A.H = H; A.dk = dk; A.dv = dv; A.L = L; A.write_state = write_state;
+  A.da = alpha ? nullptr : decay_a; A.lda = lda; A.dw = decay_w; A.dbias = decay_bias; A.inv_tau = alpha ? 0.f : 1.f / tau; A.R = rank;
   // a column's threads lie within one warp (L divides 32); a tile of value channels fills up to 256 threads,
   // and is narrower where few requests would leave SMs idle
   int VT = GLA_MAX_COMPUTE / L;

@@ -1181,20 +1181,37 @@ def channel_decay(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]
                                   T, N, R, _dt(a), _stream()), "channel_decay")
 
 
-def linear_attention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, alpha: torch.Tensor, state: torch.Tensor,
+SCAN_FORMS_DECAY = True     # steps of single tokens: the scan forms the decay from the low-rank pair itself (no decay kernel)
+
+
+def linear_attention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, alpha: Optional[torch.Tensor], state: torch.Tensor,
                           ctx, out: torch.Tensor, q_scale: float, num_heads: int, key_dim: int, value_dim: int,
-                          write_state: bool = True) -> None:
+                          write_state: bool = True, decay=None) -> None:
     """The recurrence S <- diag(alpha_t) S + k_t v_t^T, o_t = S^T (q_scale q_t) per head, over the step's
     tokens of every request, from the state its slot holds (zero for a request without context) to the
     state after its last token.  q, k [T, H dk] and v [T, H dv] in the compute type (rows may be strided),
-    alpha float32 [T, H dk], state float32 [slots, H, dv, dk], out float32 [T, H dv]."""
+    alpha float32 [T, H dk], state float32 [slots, H, dv, dk], out float32 [T, H dv].
+    A step of single tokens may leave ``alpha`` None and give ``decay`` = (a, w, bias, tau) as ``channel_decay``
+    takes them: the scan then forms alpha itself, to the same bits."""
     H, dk, dv = num_heads, key_dim, value_dim
     T = q.shape[0]
     for t, name, width in ((q, "q", H * dk), (k, "k", H * dk), (v, "v", H * dv)):
         _rows(t, f"linear_attention_scan: {name}")
         _need(t.shape == (T, width) and t.dtype == q.dtype, f"linear_attention_scan: {name} must be [T, {width}]")
-    _need(alpha.shape == (T, H * dk) and alpha.dtype == torch.float32 and alpha.is_contiguous(),
-          "linear_attention_scan: alpha must be float32 [T, H dk]")
+    da = dw = db = None
+    tau, rank = 1.0, 0
+    if alpha is None:
+        _need(decay is not None and int(ctx.max_q_len) <= 1, "linear_attention_scan: without alpha, single tokens and the decay's inputs")
+        da, dw, db, tau = decay
+        _rows(da, "linear_attention_scan: decay a")
+        rank = da.shape[1]
+        _need(da.shape[0] == T and da.dtype == q.dtype and dw.dtype == q.dtype and dw.shape == (H * dk, rank) and dw.is_contiguous(),
+              "linear_attention_scan: decay a [T, rank] and w [H dk, rank] in q's dtype")
+        _need(db is None or (db.dtype == torch.float32 and db.shape == (H * dk,) and db.is_contiguous()),
+              "linear_attention_scan: decay bias must be float32 [H dk]")
+    else:
+        _need(alpha.shape == (T, H * dk) and alpha.dtype == torch.float32 and alpha.is_contiguous(),
+              "linear_attention_scan: alpha must be float32 [T, H dk]")
     _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (H, dv, dk),
           "linear_attention_scan: state must be float32 [slots, H, dv, dk]")
     _need(out.shape == (T, H * dv) and out.dtype == torch.float32 and out.is_contiguous(),
@@ -1202,7 +1219,9 @@ def linear_attention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, alp
     _check(lib().qe_linear_attention_scan(
         _ptr(q), _ptr(k), _ptr(v), ctypes.c_long(q.stride(0)), ctypes.c_long(k.stride(0)), ctypes.c_long(v.stride(0)),
         _ptr(alpha), _ptr(state), _ptr(ctx.cu_q), _ptr(ctx.ctx_lens), _ptr(ctx.slot_ids), _ptr(out), ctypes.c_float(q_scale),
-        int(ctx.num_reqs), int(ctx.max_q_len), H, dk, dv, int(bool(write_state)), _dt(q), _stream()), "linear_attention_scan")
+        int(ctx.num_reqs), int(ctx.max_q_len), H, dk, dv, int(bool(write_state)), _dt(q), _ptr(da),
+        ctypes.c_long(da.stride(0) if da is not None else 0), _ptr(dw), _ptr(db), ctypes.c_float(tau), int(rank), _stream()),
+        "linear_attention_scan")
 
 
 _GATES = {None: 0, "silu": 1, "sigmoid": 2}

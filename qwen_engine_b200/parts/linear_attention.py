@@ -107,10 +107,15 @@ class GatedLinearAttention(Mixer):
         ops.linear(x, self.w_in, proj)
         q, k = proj[:, :kw], proj[:, kw:2 * kw]
         v, gate = proj[:, 2 * kw:2 * kw + vw], proj[:, 2 * kw + vw:2 * kw + 2 * vw]
-        alpha = ctx.arena.alloc((T, kw), torch.float32)
-        ops.channel_decay(proj[:, 2 * kw + 2 * vw:], self.w_decay, self.decay_bias, self.decay_tau, alpha)
         o = ctx.arena.alloc((T, vw), torch.float32)
-        ops.linear_attention_scan(q, k, v, alpha, cache, ctx, o, self.q_scale, H, dk, dv, write_state=write_cache)
+        if ops.SCAN_FORMS_DECAY and ctx.max_q_len <= 1:
+            # single tokens: the scan's CTAs form their head's decay themselves (one launch less in a chain of launches)
+            ops.linear_attention_scan(q, k, v, None, cache, ctx, o, self.q_scale, H, dk, dv, write_state=write_cache,
+                                      decay=(proj[:, 2 * kw + 2 * vw:], self.w_decay, self.decay_bias, self.decay_tau))
+        else:
+            alpha = ctx.arena.alloc((T, kw), torch.float32)
+            ops.channel_decay(proj[:, 2 * kw + 2 * vw:], self.w_decay, self.decay_bias, self.decay_tau, alpha)
+            ops.linear_attention_scan(q, k, v, alpha, cache, ctx, o, self.q_scale, H, dk, dv, write_state=write_cache)
         ops.head_norm_gate(o, gate, self.norm_w, self.norm_eps, inner, H, dv, gate_kind="silu", scale=scale)
 
     def forward(self, ctx: StepContext, x, cache, group, out, write_cache: bool = True) -> None:

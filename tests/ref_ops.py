@@ -192,9 +192,13 @@ def channel_decay(a, w, bias, tau, out):
     out.copy_(torch.exp(torch.nn.functional.logsigmoid(z) / tau))
 
 
-def linear_attention_scan(q, k, v, alpha, state, ctx, out, q_scale, num_heads, key_dim, value_dim, write_state=True):
+def linear_attention_scan(q, k, v, alpha, state, ctx, out, q_scale, num_heads, key_dim, value_dim, write_state=True, decay=None):
     """state [slots, H, dv, dk]; per request and head, token by token."""
     H, dk, dv = num_heads, key_dim, value_dim
+    if alpha is None:
+        a, w, bias, tau = decay
+        alpha = torch.empty(q.shape[0], H * dk, dtype=torch.float32)
+        channel_decay(a, w, bias, tau, alpha)
     cu, ctx_lens, slots = ctx.cu_q.tolist(), ctx.ctx_lens.tolist(), ctx.slot_ids.tolist()
     for r in range(len(ctx_lens)):
         a, b = cu[r], cu[r + 1]

@@ -151,6 +151,28 @@ def test_scan_long_and_a_state_that_is_read_only(ops):
     assert torch.equal(state, before)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,dk,dv,R", [(2, 16, 24, 3), (3, 128, 64, 16), (1, 10, 7, 1), (4, 64, 128, 32)])
+def test_scan_of_single_tokens_that_forms_the_decay_itself(ops, dtype, H, dk, dv, R):
+    """A step of single tokens with the decay's inputs in the place of alpha: the same bits as decay kernel + scan."""
+    g = torch.Generator().manual_seed(H + dk + R)
+    B = 5
+    wide = torch.randn(B, 2 * H * dk + H * dv + R + 2, generator=g).to(dtype).to(DEV)
+    q, k, v = wide[:, :H * dk], wide[:, H * dk:2 * H * dk], wide[:, 2 * H * dk:2 * H * dk + H * dv]
+    a = wide[:, 2 * H * dk + H * dv:2 * H * dk + H * dv + R]
+    w = torch.randn(H * dk, R, generator=g).to(dtype).to(DEV)
+    bias = (torch.randn(H * dk, generator=g) * 2).to(DEV)
+    state0 = torch.randn(B + 1, H, dv, dk, generator=g).to(DEV)
+    ctx = _ctx([1] * B, [3, 0, 9, 1, 40], [4, 0, 2, 5, 1])
+    alpha = torch.empty(B, H * dk, dtype=F32, device=DEV)
+    ops.channel_decay(a, w, bias, 4.0, alpha)
+    s1, s2 = state0.clone(), state0.clone()
+    o1, o2 = torch.empty(B, H * dv, dtype=F32, device=DEV), torch.empty(B, H * dv, dtype=F32, device=DEV)
+    ops.linear_attention_scan(q, k, v, alpha, s1, ctx, o1, dk ** -0.5, H, dk, dv)
+    ops.linear_attention_scan(q, k, v, None, s2, ctx, o2, dk ** -0.5, H, dk, dv, decay=(a, w, bias, 4.0))
+    assert torch.equal(o1, o2) and torch.equal(s1, s2)
+
+
 # ---- norm of a head with its gate, the feed-forward's activation, the embedding -------------------------------------------
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,D", [(1, 7), (3, 24), (2, 128), (6, 32)])
