@@ -80,6 +80,7 @@ class GQAAttention(Mixer):
         # output product) when any of the options above is on
         self.extended = bool(output_gate or self.distance_slopes is not None or self.value_dim != self.key_dim)
         self.inner_width = self.q_width
+        self.input_width = self.q_width + 2 * self.kv_width + (self.q_width if output_gate else 0)
         self.w_qkv = self.w_o = self.q_norm_w = self.k_norm_w = self.slopes = None
 
     def cache_spec(self):
@@ -135,14 +136,20 @@ class GQAAttention(Mixer):
     def output_weight(self):
         return self.w_o
 
+    def input_weight(self):
+        return self.w_qkv
+
     def mix_into(self, ctx: StepContext, x, cache, group, inner, write_cache: bool = True, scale: float = 1.0) -> None:
         """Everything before the output projection, as separate operations; serves every option."""
+        proj = ctx.arena.alloc((ctx.num_tokens, self.input_width), ctx.dtype)
+        ops.linear(x, self.w_qkv, proj)
+        self.mix_projected(ctx, proj, cache, group, inner, write_cache, scale)
+
+    def mix_projected(self, ctx: StepContext, proj, cache, group, inner, write_cache: bool = True, scale: float = 1.0) -> None:
         T = ctx.num_tokens
         H, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
         view = ctx.groups[group]
         n_qkv = self.q_width + 2 * self.kv_width
-        proj = ctx.arena.alloc((T, n_qkv + (self.q_width if self.output_gate else 0)), ctx.dtype)
-        ops.linear(x, self.w_qkv, proj)
         qkv = proj[:, :n_qkv]
         if self.pos is not None:
             # norm, then the part's own rotation, then the plain cache write (the order of model.py:204-208)
@@ -160,7 +167,7 @@ class GQAAttention(Mixer):
         ops.paged_attention(qkv, cache, view.block_tables, ctx, attn, self.scale, self.window or 0, H, Hkv, D,
                             slopes=self.slopes)
         if attn is not inner:
-            ops.head_norm_gate(attn, proj[:, n_qkv:] if self.output_gate else None, None, 0.0, inner, H, D,
+            ops.head_norm_gate(attn, proj[:, n_qkv:n_qkv + self.q_width] if self.output_gate else None, None, 0.0, inner, H, D,
                                gate_kind=self.output_gate, scale=scale)
 
     def forward(self, ctx: StepContext, x, cache, group, out, write_cache: bool = True) -> None:

@@ -268,9 +268,23 @@ class Mixer(Part):
     #                          everything before the output projection; ``inner`` [T, inner_width] may be a
     #                          column slice of a wider buffer (unit stride along columns); what is written
     #                          is multiplied by ``scale`` in float32 before it is rounded
+    # A mixer whose forward begins with ONE product of its input over stacked weights may offer that half apart too, so
+    # that mixers side by side run one product over all their stacked weights:
+    #   input_width            columns of that product (None: not offered)
+    #   input_weight()         the [input_width, hidden] matrix, loaded
+    #   mix_projected(ctx, proj, cache, group, inner, write_cache, scale)
+    #                          mix_into from the product's output ``proj`` [T, input_width] on (a column slice, may be changed)
     inner_width: Optional[int] = None
+    input_width: Optional[int] = None
 
     def output_weight(self) -> torch.Tensor:
+        raise NotImplementedError
+
+    def input_weight(self) -> torch.Tensor:
+        raise NotImplementedError
+
+    def mix_projected(self, ctx: "StepContext", proj: torch.Tensor, cache, group, inner: torch.Tensor,
+                      write_cache: bool = True, scale: float = 1.0) -> None:
         raise NotImplementedError
 
     def mix_into(self, ctx: "StepContext", x: torch.Tensor, cache, group, inner: torch.Tensor,

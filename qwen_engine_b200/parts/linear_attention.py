@@ -58,6 +58,7 @@ class GatedLinearAttention(Mixer):
         self.q_scale = float(key_dim) ** -0.5
         self.w_in = self.w_decay = self.decay_bias = self.norm_w = self.w_o = None
         self.rank = decay_rank
+        self.input_width = None if decay_rank is None else 2 * self.k_width + 2 * self.v_width + decay_rank    # (known at load otherwise)
 
     def cache_spec(self):
         # a head's state is kept with the key channels of a value channel side by side (the scan's threads
@@ -86,6 +87,7 @@ class GatedLinearAttention(Mixer):
         if a1.shape[0] != a2.shape[1]:
             raise ValueError(f"{prefix}: the decay's pair does not fit: {tuple(a1.shape)} and {tuple(a2.shape)}")
         self.rank = int(a1.shape[0])
+        self.input_width = 2 * self.k_width + 2 * self.v_width + self.rank
         # q, k, v, the gate and the first half of the pair as rows of one matrix: one product gives them all
         stacked = torch.cat([source.get(prefix + n[x]) for x in ("q", "k", "v", "gate")] + [a1], dim=0)
         self.w_in = ops.prepare_matrix(stacked.to(dtype).to(device))
@@ -100,11 +102,17 @@ class GatedLinearAttention(Mixer):
     def output_weight(self):
         return self.w_o
 
+    def input_weight(self):
+        return self.w_in
+
     def mix_into(self, ctx: StepContext, x, cache, group, inner, write_cache: bool = True, scale: float = 1.0) -> None:
+        proj = ctx.arena.alloc((ctx.num_tokens, self.input_width), ctx.dtype)
+        ops.linear(x, self.w_in, proj)
+        self.mix_projected(ctx, proj, cache, group, inner, write_cache, scale)
+
+    def mix_projected(self, ctx: StepContext, proj, cache, group, inner, write_cache: bool = True, scale: float = 1.0) -> None:
         T, H, dk, dv = ctx.num_tokens, self.num_heads, self.key_dim, self.value_dim
         kw, vw = self.k_width, self.v_width
-        proj = ctx.arena.alloc((T, 2 * kw + 2 * vw + self.rank), ctx.dtype)
-        ops.linear(x, self.w_in, proj)
         q, k = proj[:, :kw], proj[:, kw:2 * kw]
         v, gate = proj[:, 2 * kw:2 * kw + vw], proj[:, 2 * kw + vw:2 * kw + 2 * vw]
         o = ctx.arena.alloc((T, vw), torch.float32)

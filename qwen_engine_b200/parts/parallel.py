@@ -10,7 +10,10 @@ two halves apart (``Mixer.mix_into`` / ``output_weight``), the branches write
 their inner rows, already multiplied by their scale in float32, side by side
 into one buffer and ONE product over the output matrices joined along K gives
 the sum: no product per branch, no add kernel, and each value is rounded once.
-Otherwise the branches run whole and their outputs are added.
+Otherwise the branches run whole and their outputs are added.  In the same
+way, branches that begin with one product of the input over stacked weights
+(``Mixer.input_weight`` / ``mix_projected``) share ONE product over all their
+stacked weights: the input is read once and the weights stream in one launch.
 """
 from __future__ import annotations
 
@@ -24,7 +27,7 @@ from .base import Mixer, PartSpec, StepContext, register
 
 @register("mixer", "parallel_mixers")
 class ParallelMixers(Mixer):
-    takes_lazy_input = False      # every branch reads x: it is formed once
+    takes_lazy_input = False      # every branch reads x: it is formed once (and goes to ops.linear as a tensor)
     writes_through_linear = True  # out is the out of the one joined product (or of the first branch's last product)
 
     def __init__(self, branches: Sequence[PartSpec], scales: Sequence[float], prefixes: Sequence[str]):
@@ -36,6 +39,7 @@ class ParallelMixers(Mixer):
         self.joined = all(b.inner_width is not None for b in self.branches)
         self.inner_width = sum(b.inner_width for b in self.branches) if self.joined else None
         self.w_o: Optional[torch.Tensor] = None
+        self.w_in: Optional[torch.Tensor] = None      # the branches' stacked input weights, stacked once more (if all offer them)
         self._n_caches = [len(b.cache_specs()) for b in self.branches]
 
     @property
@@ -57,9 +61,13 @@ class ParallelMixers(Mixer):
         if self.joined:
             # [hidden, inner_1 + inner_2 + ...]: the sum over branches happens inside the product
             self.w_o = ops.prepare_matrix(torch.cat([b.output_weight() for b in self.branches], dim=1))
+            # (every branch's columns then begin on a 16-byte boundary of a row whose stride is a multiple of 16 bytes,
+            # which the attention kernels ask of their queries; widths that do not allow it keep a product per branch)
+            if all(b.input_width is not None and b.input_width % 8 == 0 for b in self.branches):
+                self.w_in = ops.prepare_matrix(torch.cat([b.input_weight() for b in self.branches], dim=0))
 
     def first_weights(self):
-        return self.branches[0].first_weights()
+        return self.w_in if self.w_in is not None else self.branches[0].first_weights()
 
     def output_weight(self):
         return self.w_o
@@ -80,10 +88,18 @@ class ParallelMixers(Mixer):
         return out
 
     def mix_into(self, ctx: StepContext, x, cache, group, inner, write_cache: bool = True, scale: float = 1.0) -> None:
-        at = 0
+        at = col = 0
+        proj = None
+        if self.w_in is not None:
+            proj = ctx.arena.alloc((ctx.num_tokens, self.w_in.shape[0]), ctx.dtype)
+            ops.linear(x, self.w_in, proj)
         for b, s, (c, g) in zip(self.branches, self.scales, self._caches(cache, group)):
             mark = ctx.arena.mark()
-            b.mix_into(ctx, x, c, g, inner[:, at:at + b.inner_width], write_cache, scale * s)
+            if proj is not None:
+                b.mix_projected(ctx, proj[:, col:col + b.input_width], c, g, inner[:, at:at + b.inner_width], write_cache, scale * s)
+                col += b.input_width
+            else:
+                b.mix_into(ctx, x, c, g, inner[:, at:at + b.inner_width], write_cache, scale * s)
             ctx.arena.release(mark)
             at += b.inner_width
 
