@@ -307,10 +307,11 @@ def test_attention_with_window_and_distance_bias(ops, dtype, flash, Hq, Hkv, D, 
                                                     ([1, 1, 1, 1], [300, 17, 512, 64], "decode_attention_mma"),
                                                     ([2, 1], [200, 90], "decode_attention_mma")])
 @pytest.mark.parametrize("window", [64, 200])
-def test_biased_attention_on_the_kernels_of_head_size_128(ops, q_lens, ctx_lens, kernel, window):
+@pytest.mark.parametrize("Hq,Hkv", [(8, 2), (4, 4), (16, 2)])
+def test_biased_attention_on_the_kernels_of_head_size_128(ops, q_lens, ctx_lens, kernel, window, Hq, Hkv):
     """Head size 128: prompt portions on the tcgen05 kernel, decoded tokens on the warp-pipelined kernel, both with
     the distance bias and a window that ends inside their key steps."""
-    Hq, Hkv, D, P = 8, 2, 128, 16
+    D, P = 128, 16
     slopes = [2.0 ** (-8.0 * (h + 1) / Hq) for h in range(Hq)]
     qkv, cache, table = _attention_case(Hq, Hkv, D, P, q_lens, ctx_lens, BF16, 5 + len(q_lens))
     scale = 1.0 / math.sqrt(D)
