@@ -541,6 +541,72 @@ __global__ void head_norm_gate_kernel(const TI* __restrict__ o, long ldo, const 
   }
 }
 
+// The same for bfloat16 gates and outputs where a head is a multiple of 128 channels and everything lies on 16-byte
+// boundaries: a lane takes four neighbouring channels of every 128 (16 bytes of float32 o, 8 bytes of gate and of
+// output), all loads on their way before the sum of squares.
+template <typename TI, int NV>
+__global__ void head_norm_gate_vec_kernel(const TI* __restrict__ o, long ldo, const __nv_bfloat16* __restrict__ g, long ldg,
+                                          const float* __restrict__ w, float eps, __nv_bfloat16* __restrict__ out, long ldout,
+                                          float scale, int gate, long items, int H) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int D = NV * 128;
+  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long item = (long)blockIdx.x * warps + warp;
+  if (item >= items) return;
+  const long t = item / H;
+  const int h = (int)(item - t * H);
+  const TI* x = o + (size_t)t * ldo + (size_t)h * D;
+  float v[NV][4], gv[NV][4];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int d = i * 128 + lane * 4;
+    if constexpr (sizeof(TI) == 4) {
+      const float4 f = *reinterpret_cast<const float4*>(x + d);
+      v[i][0] = f.x; v[i][1] = f.y; v[i][2] = f.z; v[i][3] = f.w;
+    } else {
+      const uint2 r = *reinterpret_cast<const uint2*>(x + d);
+      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.x));
+      const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.y));
+      v[i][0] = a.x; v[i][1] = a.y; v[i][2] = b.x; v[i][3] = b.y;
+    }
+    if (g) {
+      const uint2 r = *reinterpret_cast<const uint2*>(g + (size_t)t * ldg + (size_t)h * D + d);
+      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.x));
+      const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.y));
+      gv[i][0] = a.x; gv[i][1] = a.y; gv[i][2] = b.x; gv[i][3] = b.y;
+    }
+  }
+  float rstd = 1.f;
+  if (w) {
+    // (the sum runs over a lane's channels in the order of the channels, then over the lanes: fixed by the sizes)
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+#pragma unroll
+      for (int u = 0; u < 4; ++u) ss = fmaf(v[i][u], v[i][u], ss);
+    ss = warp_sum(ss);
+    rstd = rsqrtf(ss / (float)D + eps);
+  }
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int d = i * 128 + lane * 4;
+    float r4[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      float val = v[i][u] * rstd;
+      if (w) val *= w[d + u];
+      if (g) val *= gate_value(gv[i][u], gate);
+      r4[u] = val * scale;
+    }
+    __nv_bfloat162 lo = __floats2bfloat162_rn(r4[0], r4[1]), hi = __floats2bfloat162_rn(r4[2], r4[3]);
+    uint2 st;
+    st.x = *reinterpret_cast<uint32_t*>(&lo);
+    st.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(out + (size_t)t * ldout + (size_t)h * D + d) = st;
+  }
+}
+
 extern "C" int qe_head_norm_gate(const void* o, long ldo, int o_f32, const void* g, long ldg, const float* w, float eps,
                                  void* out, long ldout, float scale, int gate, int T, int H, int D, int dtype,
                                  cudaStream_t stream) {
@@ -548,6 +614,16 @@ extern "C" int qe_head_norm_gate(const void* o, long ldo, int o_f32, const void*
   const long items = (long)T * H;
   const int warps = 8;
   const unsigned blocks = (unsigned)((items + warps - 1) / warps);
+  if (dtype == QE_DTYPE_BF16 && (D == 128 || D == 256) && ldo % 4 == 0 && ldg % 4 == 0 && ldout % 4 == 0 &&
+      (((uintptr_t)o & 15) | ((uintptr_t)g & 7) | ((uintptr_t)out & 7)) == 0) {
+#define HNGV(TI, NV) qe_launch(head_norm_gate_vec_kernel<TI, NV>, dim3(blocks), dim3(warps * 32), 0, stream, (const TI*)o, ldo, \
+                               (const __nv_bfloat16*)g, ldg, w, eps, (__nv_bfloat16*)out, ldout, scale, gate, items, H)
+    if (o_f32) { if (D == 128) HNGV(float, 1); else HNGV(float, 2); }
+    else { if (D == 128) HNGV(__nv_bfloat16, 1); else HNGV(__nv_bfloat16, 2); }
+#undef HNGV
+    QE_CHECK_LAUNCH("head_norm_gate");
+    return 0;
+  }
 #define HNG(TT, TI) qe_launch(head_norm_gate_kernel<TT, TI>, dim3(blocks), dim3(warps * 32), 0, stream, (const TI*)o, ldo, \
                               (const TT*)g, ldg, w, eps, (TT*)out, ldout, scale, gate, items, H, D)
   if (dtype == QE_DTYPE_F32) HNG(float, float);

@@ -175,15 +175,15 @@ def test_scan_of_single_tokens_that_forms_the_decay_itself(ops, dtype, H, dk, dv
 
 # ---- norm of a head with its gate, the feed-forward's activation, the embedding -------------------------------------------
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("H,D", [(1, 7), (3, 24), (2, 128), (6, 32)])
+@pytest.mark.parametrize("H,D", [(1, 7), (3, 24), (2, 128), (6, 32), (3, 256)])
 def test_head_norm_gate(ops, dtype, H, D):
     g = torch.Generator().manual_seed(H * D)
     T = 21
     x = torch.randn(T, H * D, generator=g) * 3
-    wide = torch.randn(T, H * D + 9, generator=g).to(dtype)
+    wide = torch.randn(T, H * D + 12, generator=g).to(dtype)      # (strides that let heads of 128 and 256 take 16-byte pieces)
     gate = wide[:, 4:4 + H * D]
     w = torch.randn(D, generator=g)
-    buf = torch.zeros(T, 2 * H * D + 3, dtype=dtype, device=DEV)
+    buf = torch.zeros(T, 2 * H * D + 4, dtype=dtype, device=DEV)
     out = buf[:, H * D:2 * H * D]                                   # a column slice of a wider buffer
     ops.head_norm_gate(x.to(DEV), wide.to(DEV)[:, 4:4 + H * D], w.to(DEV), 1e-5, out, H, D, gate_kind="silu", scale=0.6)
     want = torch.cat([plain.norm_plain(x[:, h * D:(h + 1) * D].double(), w.double(), 1e-5) for h in range(H)], dim=1)
