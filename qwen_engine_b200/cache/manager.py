@@ -98,7 +98,7 @@ class CacheManager:
             if g.is_paged:
                 n = (num_pages_of_group or {}).get(g.index, num_pages)
                 g.pool = PagePool(n, page_size, self.prefix_cache)
-                shape = (len(g.cache_slots), n, 2, g.spec.num_kv_heads, page_size, g.spec.head_dim)
+                shape = (len(g.cache_slots), n, g.spec.planes, g.spec.num_kv_heads, page_size, g.spec.head_dim)
                 g.tensor = torch.zeros(shape, dtype=dtype, device=self.device)
                 if poison is not False and poison is not None:
                     g.tensor.fill_(float("nan") if poison is True else float(poison))
@@ -114,7 +114,7 @@ class CacheManager:
 
     # ---- views for the parts ---------------------------------------------------------
     def layer_view(self, cache_slot: int) -> Optional[torch.Tensor]:
-        """The tensor of one cache slot: [pages, 2, kv heads, page size, head dim] for
+        """The tensor of one cache slot: [pages, planes, kv heads, page size, head dim] for
         paged keys and values, [state slots, *shape] for state of fixed size."""
         if cache_slot not in self.group_of_slot:
             return None

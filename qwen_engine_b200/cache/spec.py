@@ -13,12 +13,15 @@ class PagedKVSpec:
 
     ``window`` = None keeps every key; a number keeps only the last ``window``
     keys of a request alive: pages that every later query has passed are given
-    back while the request still runs.
+    back while the request still runs.  ``planes`` = 1: a page holds one
+    plane per kv head instead of a key plane and a value plane (a latent
+    cache, whose values are channels of its keys).
     """
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    planes: int = 2
 
     @property
     def kind(self) -> str:

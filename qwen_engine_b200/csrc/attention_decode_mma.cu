@@ -104,8 +104,8 @@ decode_attention_mma_kernel(FaArgs A, long long prefetch_delta, int early_issue,
 
   const int* __restrict__ table = A.block_tables + (size_t)req * A.max_blocks;
   const int page_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
-  const size_t page_stride = (size_t)2 * Hkv * page_size * D;
-  const size_t v_off = (size_t)Hkv * page_size * D;
+  const size_t page_stride = (size_t)(A.kv_planes == 1 ? 1 : 2) * Hkv * page_size * D;
+  const size_t v_off = A.kv_planes == 1 ? 0 : (size_t)Hkv * page_size * D;
   const __nv_bfloat16* head_base = A.pages + (size_t)hkv * page_size * D;
   // a group that starts at a multiple of 16 keys lies in one page when pages are multiples of 16 keys
   const bool one_page = page_shift >= 4 && (kv_begin & 15) == 0;
@@ -467,7 +467,8 @@ extern "C" int qe_decode_attention_mma_supported(int Hq, int Hkv, int D, int max
 extern "C" int qe_decode_attention_mma(const void* q, long q_stride, const void* pages, const void* prefetch_pages, const int* block_tables,
                                        int max_blocks, const int* items, int n_items, void* out, float* part_acc,
                                        float* part_ml, int part_rows, int* counters, int max_rows, int cluster, int wide, float scale,
-                                       int window, int Hq, int Hkv, int D, int page_size, const float* slopes, cudaStream_t stream) {
+                                       int window, int Hq, int Hkv, int D, int page_size, const float* slopes, int kv_planes,
+                                       cudaStream_t stream) {
   if (n_items <= 0) return 0;
   if (!qe_decode_attention_mma_supported(Hq, Hkv, D, max_rows))
     QE_REFUSE("decode_attention_mma: heads %d/%d, head_dim %d, %d rows are not supported", Hq, Hkv, D, max_rows);
@@ -477,7 +478,7 @@ extern "C" int qe_decode_attention_mma(const void* q, long q_stride, const void*
   if (part_acc && counters == nullptr && !cluster) QE_REFUSE("decode_attention_mma: parts need the counters");
   FaArgs fa{(const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)pages, block_tables, max_blocks, items,
             (__nv_bfloat16*)out, part_acc, part_ml, part_rows, counters, scale * 1.4426950408889634f, window, Hq, Hkv,
-            page_size, slopes};
+            page_size, slopes, kv_planes};
   if (cluster == 0) return launch_decode_mma<false>(fa, delta, n_items, Hkv, 0, wide, max_rows, stream);
   if ((cluster != 2 && cluster != 4 && cluster != 8) || n_items % cluster)
     QE_REFUSE("decode_attention_mma: %d items cannot form clusters of %d", n_items, cluster);

@@ -260,6 +260,7 @@ struct FaArgs {
   float* part_acc; float* part_ml; int part_rows;
   int* counters; float scale_log2; int window, Hq, Hkv, page_size;
   const float* slopes;      // null, or float32 [Hq]: slopes[h] * (position - key) is taken off the score (last: may be left out)
+  int kv_planes;            // 1: a page holds one plane per kv head and the values are its channels (a latent cache); else keys and values apart
 };
 
 // The work of one CTA (work item `item_idx`, kv head `hkv`) by 256 threads; `smem_raw`: the dynamic
@@ -333,8 +334,8 @@ __device__ __forceinline__ void flash_attention_cta(const FaArgs& A, int item_id
     const int* table = block_tables + (size_t)req * max_blocks;
     // address arithmetic of the gather, hoisted: a page's stride, this head's offset in a page, K -> V
     const int page_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
-    const size_t page_stride = (size_t)2 * Hkv * page_size * D;
-    const size_t v_off = (size_t)Hkv * page_size * D;
+    const size_t page_stride = (size_t)(A.kv_planes == 1 ? 1 : 2) * Hkv * page_size * D;
+    const size_t v_off = A.kv_planes == 1 ? 0 : (size_t)Hkv * page_size * D;
     const __nv_bfloat16* head_base = pages + (size_t)hkv * page_size * D;
     bool waited = false;
     auto wait_and_fetch_q = [&]() {

@@ -26,7 +26,7 @@ attention_generic_kernel(const T* __restrict__ q, long q_stride, const T* __rest
                          const int* __restrict__ block_tables, int max_blocks,
                          const int* __restrict__ cu_q, const int* __restrict__ ctx_lens,
                          const int* __restrict__ tiles, T* __restrict__ out, float scale, int window,
-                         int Hq, int Hkv, int D, int page_size, const float* __restrict__ slopes) {
+                         int Hq, int Hkv, int D, int page_size, const float* __restrict__ slopes, int kv_planes) {
   extern __shared__ float smem[];
   pdl_launch_dependents();
   pdl_wait();
@@ -73,9 +73,10 @@ attention_generic_kernel(const T* __restrict__ q, long q_stride, const T* __rest
       float kvl = 0.f, vvl = 0.f;
       if (kj >= kv_begin && kj < kv_end) {
         const int page = table[kj / page_size];
-        const size_t base = ((((size_t)page * 2) * Hkv + hkv) * page_size + (kj % page_size)) * D + d;
+        // (kv_planes 1: a page holds one plane per kv head, and the values are its channels)
+        const size_t base = ((((size_t)page * kv_planes) * Hkv + hkv) * page_size + (kj % page_size)) * D + d;
         kvl = to_f32(pages[base]);
-        vvl = to_f32(pages[base + (size_t)Hkv * page_size * D]);
+        vvl = kv_planes == 1 ? kvl : to_f32(pages[base + (size_t)Hkv * page_size * D]);
       }
       ks[j * Dp + d] = kvl;
       vs[j * D + d] = vvl;
@@ -130,7 +131,7 @@ extern "C" int qe_paged_attention_generic(const void* q, long q_stride, const vo
                                           const int* block_tables, int max_blocks, const int* cu_q,
                                           const int* ctx_lens, const int* tiles, int n_tiles, void* out,
                                           float scale, int window, int Hq, int Hkv, int D, int page_size,
-                                          int dtype, const float* slopes, cudaStream_t stream) {
+                                          int dtype, const float* slopes, int kv_planes, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (D > AG_MAX_D || D < 1) QE_REFUSE("paged_attention: head_dim %d is outside 1..%d", D, AG_MAX_D);
   if (Hkv < 1 || Hq % Hkv) QE_REFUSE("paged_attention: %d query heads do not group over %d kv heads", Hq, Hkv);
@@ -149,11 +150,11 @@ extern "C" int qe_paged_attention_generic(const void* q, long q_stride, const vo
   if (dtype == QE_DTYPE_F32) {
     qe_launch(attention_generic_kernel<float>, grid, dim3(AG_WARPS * 32), smem, stream,
         (const float*)q, q_stride, (const float*)pages, block_tables, max_blocks, cu_q, ctx_lens, tiles,
-        (float*)out, scale, window, Hq, Hkv, D, page_size, slopes);
+        (float*)out, scale, window, Hq, Hkv, D, page_size, slopes, kv_planes == 1 ? 1 : 2);
   } else if (dtype == QE_DTYPE_BF16) {
     qe_launch(attention_generic_kernel<__nv_bfloat16>, grid, dim3(AG_WARPS * 32), smem, stream,
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)pages, block_tables, max_blocks, cu_q, ctx_lens,
-        tiles, (__nv_bfloat16*)out, scale, window, Hq, Hkv, D, page_size, slopes);
+        tiles, (__nv_bfloat16*)out, scale, window, Hq, Hkv, D, page_size, slopes, kv_planes == 1 ? 1 : 2);
   } else QE_REFUSE("paged_attention: unknown dtype %d", dtype);
   QE_CHECK_LAUNCH("paged_attention_generic");
   return 0;

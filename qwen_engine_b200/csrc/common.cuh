@@ -63,6 +63,20 @@ __device__ __forceinline__ float gate_act_fast(float g, int act) {
   return __fdividef(g, 1.f + __expf(-g));
 }
 
+// A gated feed-forward's value from its gate g and its up projection u.  act 0 and 1: act(g) * u as above.  Any
+// other value of act is the bit pattern of a float32 limit L > 0 (every such pattern is an integer above 1) and
+// names the limited form: g' = min(g, L), u' = clamp(u, -L, L), g' * sigmoid(1.702 g') * (u' + 1).
+#define QE_GLU_SIGMOID_SLOPE 1.702f
+__device__ __forceinline__ float glu_fast(float g, float u, int act) {
+  if (act > 1) {
+    const float lim = __int_as_float(act);
+    g = fminf(g, lim);
+    u = fminf(fmaxf(u, -lim), lim);
+    return __fdividef(g, 1.f + __expf(-QE_GLU_SIGMOID_SLOPE * g)) * (u + 1.f);
+  }
+  return gate_act_fast(g, act) * u;
+}
+
 // ---- programmatic dependent launch --------------------------------------------------------------------
 // Kernels of a step form a chain on one stream.  Launched with the attribute below, a kernel may
 // start while its predecessor is still running; it must call pdl_wait() before it touches anything

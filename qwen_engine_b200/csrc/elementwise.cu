@@ -266,6 +266,16 @@ __device__ __forceinline__ float gate_act(float g, int act) {
   if (act == 1) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
   return g / (1.f + expf(-g));
 }
+// the value of a gated feed-forward; act beyond 1 is the bit pattern of the limit of the limited form (common.cuh: glu_fast)
+__device__ __forceinline__ float glu_value(float g, float u, int act) {
+  if (act > 1) {
+    const float lim = __int_as_float(act);
+    g = fminf(g, lim);
+    u = fminf(fmaxf(u, -lim), lim);
+    return g / (1.f + expf(-QE_GLU_SIGMOID_SLOPE * g)) * (u + 1.f);
+  }
+  return gate_act(g, act) * u;
+}
 
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int I, size_t total, int act) {
@@ -276,7 +286,7 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
     const int i = (int)(e - t * I);
     const float g = to_f32(gate_up[t * 2 * I + i]);
     const float u = to_f32(gate_up[t * 2 * I + I + i]);
-    out[e] = from_f32<T>(gate_act(g, act) * u);
+    out[e] = from_f32<T>(glu_value(g, u, act));
   }
 }
 
@@ -301,13 +311,13 @@ __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up
     bf16x8_to_f32(rg0, g);
     bf16x8_to_f32(ru0, u);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) g[k] = gate_act_fast(g[k], act) * u[k];
+    for (int k = 0; k < 8; ++k) g[k] = glu_fast(g[k], u[k], act);
     *reinterpret_cast<uint4*>(out + t0 * I + i0) = f32_to_bf16x8(g);
     if (two) {
       bf16x8_to_f32(rg1, g);
       bf16x8_to_f32(ru1, u);
 #pragma unroll
-      for (int k = 0; k < 8; ++k) g[k] = gate_act_fast(g[k], act) * u[k];
+      for (int k = 0; k < 8; ++k) g[k] = glu_fast(g[k], u[k], act);
       *reinterpret_cast<uint4*>(out + t1 * I + i1) = f32_to_bf16x8(g);
     }
   }
@@ -318,7 +328,7 @@ extern "C" int qe_silu_mul(const void* gate_up, void* out, int T, int I, int dty
   return act_mul_launch(gate_up, out, T, I, dtype, 0, stream);
 }
 extern "C" int qe_act_mul(const void* gate_up, void* out, int T, int I, int dtype, int act, cudaStream_t stream) {
-  if (act < 0 || act > 1) QE_REFUSE("act_mul: unknown activation %d", act);
+  if (act < 0) QE_REFUSE("act_mul: unknown activation %d", act);
   return act_mul_launch(gate_up, out, T, I, dtype, act, stream);
 }
 static int act_mul_launch(const void* gate_up, void* out, int T, int I, int dtype, int act, cudaStream_t stream) {

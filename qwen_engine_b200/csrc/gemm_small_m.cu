@@ -305,7 +305,7 @@ gemm_small_m_swiglu_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloa
 
 // act[M, I] = silu(x · w[:I]^T) * (x · w[I:]^T) for the stacked weights w [2 I, K], M <= 16 rows, bfloat16: a CTA
 // takes the gate rows and the up rows of the same 16 columns, so the activation never exists as gate and up in memory.
-// gate_act: 0 silu, 1 the tanh form of gelu.
+// gate_act: 0 silu, 1 the tanh form of gelu, else the bits of the limit of the limited form (common.cuh: glu_fast).
 extern "C" int qe_linear_small_m_swiglu(const void* x, const void* w, void* act, int M, int I, int K, int gate_act, cudaStream_t stream) {
   FuseArgs na{};
   na.next_w = g_next_w;

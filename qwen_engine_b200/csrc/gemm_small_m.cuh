@@ -404,7 +404,7 @@ __device__ __forceinline__ void gsm_cta_swiglu(const __nv_bfloat16* __restrict__
       su += red[((size_t)(nwarps + wi) * 16 + i) * MW + m];
     }
     const float gb = __bfloat162float(__float2bfloat16_rn(sg)), ub = __bfloat162float(__float2bfloat16_rn(su));
-    act[(size_t)m * I + n] = __float2bfloat16_rn(gate_act_fast(gb, gate_act) * ub);
+    act[(size_t)m * I + n] = __float2bfloat16_rn(glu_fast(gb, ub, gate_act));
   }
   QE_TL_MARK(3);
 }

@@ -328,8 +328,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
 #pragma unroll
             for (int j = 0; j < 32; j += 2) {
               const float g0 = __uint_as_float(g[q][j]), g1 = __uint_as_float(g[q][j + 1]);
-              __nv_bfloat162 pj = __floats2bfloat162_rn(gate_act_fast(g0, gate_act) * __uint_as_float(u[q][j]),
-                                                        gate_act_fast(g1, gate_act) * __uint_as_float(u[q][j + 1]));
+              __nv_bfloat162 pj = __floats2bfloat162_rn(glu_fast(g0, __uint_as_float(u[q][j]), gate_act),
+                                                        glu_fast(g1, __uint_as_float(u[q][j + 1]), gate_act));
               pk[16 * q + (j >> 1)] = *reinterpret_cast<uint32_t*>(&pj);
             }
           const int r_first = m0 + quarter * 32, c0 = ch * WC;
@@ -353,7 +353,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               const float gv = __uint_as_float(g[j]);
-              if (i0 + c0 + j < I) dst[j] = from_f32<TOut>(gate_act_fast(gv, gate_act) * __uint_as_float(u[j]));
+              if (i0 + c0 + j < I) dst[j] = from_f32<TOut>(glu_fast(gv, __uint_as_float(u[j]), gate_act));
             }
           }
         }
@@ -724,7 +724,7 @@ extern "C" int qe_linear_tcgen05_pair(const void* x, const void* w, void* out, i
 
 // out[M, I] = silu(x · w[:I]^T) * (x · w[I:]^T) for the stacked gate and up weights w [2 I, K] (see SWIGLU
 // above).  Returns 0 when run, 1 when refused, 2 on a launch error.
-// gate_act: 0 silu, 1 the tanh form of gelu.
+// gate_act: 0 silu, 1 the tanh form of gelu, else the bits of the limit of the limited form (common.cuh: glu_fast).
 extern "C" int qe_linear_swiglu_tcgen05_pair(const void* x, const void* w, void* out, int M, int I, int K, int out_f32,
                                              int gate_act, cudaStream_t stream) {
   if (M <= 0 || I <= 0) return 0;

@@ -27,7 +27,8 @@
 template <typename T>
 __global__ void __launch_bounds__(DEC_COLS)
 channel_decay_kernel(const T* __restrict__ a, long lda, const T* __restrict__ w, const float* __restrict__ bias,
-                     float inv_tau, float* __restrict__ out, int T_tokens, int N, int R) {
+                     float inv_tau, float* __restrict__ out, int T_tokens, int N, int R,
+                     const float* __restrict__ log_rate, int per_rate) {
   extern __shared__ float smem[];
   float* ws = smem;                          // [DEC_COLS][R + 1]
   float* as = ws + DEC_COLS * (R + 1);       // [DEC_ROWS][R]
@@ -48,20 +49,29 @@ channel_decay_kernel(const T* __restrict__ a, long lda, const T* __restrict__ w,
   if (n >= N) return;
   const float b = bias ? bias[n] : 0.f;
   const float* wr = ws + threadIdx.x * (R + 1);
+  // the second form: exp(-rate softplus(z)) with one rate = exp(log_rate) per `per_rate` neighbouring channels
+  const float rate = log_rate ? expf(log_rate[n / per_rate]) : 0.f;
   for (int t = 0; t < rows; ++t) {
     float z = b;
     const float* ar = as + t * R;
     for (int r = 0; r < R; ++r) z = fmaf(ar[r], wr[r], z);
-    const float logsig = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
-    out[(size_t)(t0 + t) * N + n] = expf(logsig * inv_tau);
+    if (log_rate) {
+      const float softplus = fmaxf(z, 0.f) + log1pf(expf(-fabsf(z)));
+      out[(size_t)(t0 + t) * N + n] = expf(-rate * softplus);
+    } else {
+      const float logsig = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
+      out[(size_t)(t0 + t) * N + n] = expf(logsig * inv_tau);
+    }
   }
 }
 
+// log_rate null: out = sigmoid(z)^(1/tau).  log_rate float32 [N / per_rate]: out = exp(-exp(log_rate[n / per_rate]) softplus(z)).
 extern "C" int qe_channel_decay(const void* a, long lda, const void* w, const float* bias, float tau, float* out,
-                                int T, int N, int R, int dtype, cudaStream_t stream) {
+                                int T, int N, int R, int dtype, const float* log_rate, int per_rate, cudaStream_t stream) {
   if (T <= 0 || N <= 0) return 0;
   if (R < 1 || R > 256) QE_REFUSE("channel_decay: rank %d is outside 1..256", R);
-  if (!(tau > 0.f)) QE_REFUSE("channel_decay: tau must be positive");
+  if (!log_rate && !(tau > 0.f)) QE_REFUSE("channel_decay: tau must be positive");
+  if (log_rate && (per_rate < 1 || N % per_rate)) QE_REFUSE("channel_decay: %d channels do not share rates in groups of %d", N, per_rate);
   const size_t smem = ((size_t)DEC_COLS * (R + 1) + (size_t)DEC_ROWS * R) * sizeof(float);
   static bool configured = false;
   if (!configured) {
@@ -74,10 +84,10 @@ extern "C" int qe_channel_decay(const void* a, long lda, const void* w, const fl
   dim3 grid((N + DEC_COLS - 1) / DEC_COLS, (T + DEC_ROWS - 1) / DEC_ROWS);
   if (dtype == QE_DTYPE_F32)
     qe_launch(channel_decay_kernel<float>, grid, dim3(DEC_COLS), smem, stream, (const float*)a, lda, (const float*)w, bias,
-              1.f / tau, out, T, N, R);
+              log_rate ? 0.f : 1.f / tau, out, T, N, R, log_rate, per_rate);
   else if (dtype == QE_DTYPE_BF16)
     qe_launch(channel_decay_kernel<__nv_bfloat16>, grid, dim3(DEC_COLS), smem, stream, (const __nv_bfloat16*)a, lda,
-              (const __nv_bfloat16*)w, bias, 1.f / tau, out, T, N, R);
+              (const __nv_bfloat16*)w, bias, log_rate ? 0.f : 1.f / tau, out, T, N, R, log_rate, per_rate);
   else QE_REFUSE("channel_decay: unknown dtype %d", dtype);
   QE_CHECK_LAUNCH("channel_decay");
   return 0;
@@ -103,6 +113,7 @@ struct GlaArgs {
   // single tokens may bring the decay's inputs instead of alpha: alpha = exp(logsigmoid(a . w[c] + bias[c]) / tau)
   const void* da; long lda; const void* dw; const float* dbias; float inv_tau; int R;
   int fast;                                           // ... and a chunk is at most 8 pieces a producer
+  const float* head_decay;                            // null, or [H]: alpha is this one number for every token and key channel of a head
 };
 
 // index of key channel c in a staged row: blocks of DC channels, 4 floats of padding between them (banks)
@@ -155,6 +166,7 @@ gla_scan_kernel(GlaArgs A) {
   const T* k = (const T*)A.k + (size_t)head * dk;
   const T* v = (const T*)A.v + (size_t)head * dv;
   const float* al = A.alpha + (size_t)head * dk;
+  const float hd = A.head_decay ? A.head_decay[head] : 0.f;
   const int n_chunks = (n + A.chunk - 1) / A.chunk;
   const int ptid = tid - n_compute, n_prod = blockDim.x - n_compute;
   const int padded = L * DC;
@@ -172,12 +184,12 @@ gla_scan_kernel(GlaArgs A) {
       float* dst = b + (size_t)t * tok_w;
       if (x < 3 * padded) {
         const int which = x / padded, c = x - which * padded;
-        if (which == 2 && c < dk && A.alpha == nullptr) continue;      // the kernel forms this decay itself, below
+        if (which == 2 && c < dk && A.alpha == nullptr && A.head_decay == nullptr) continue;      // the kernel forms this decay itself, below
         float val;
         if (c >= dk) val = which == 2 ? 1.f : 0.f;                     // channels beyond the head: nothing in, nothing out
         else if (which == 0) val = to_f32(q[row * A.ldq + c]) * A.q_scale;
         else if (which == 1) val = to_f32(k[row * A.ldk + c]);
-        else val = al[row * ((size_t)H * dk) + c];
+        else val = A.head_decay ? hd : al[row * ((size_t)H * dk) + c];
         dst[which * row_w + gla_pad<DC>(c)] = val;
       } else {
         const int jj = x - 3 * padded;
@@ -217,13 +229,14 @@ gla_scan_kernel(GlaArgs A) {
     }
   };
   auto fetch = [&](int kind, int off, size_t row) -> uint4 {
+    if (kind == 2 && A.head_decay) { const unsigned u = __float_as_uint(hd); return make_uint4(u, u, u, u); }
     if (kind > 3 || (kind == 2 && A.alpha == nullptr)) return make_uint4(0, 0, 0, 0);
     const char* base = kind == 0 ? base_of[0] : kind == 1 ? base_of[1] : kind == 2 ? base_of[2] : base_of[3];
     const long rb = kind == 0 ? row_bytes_of[0] : kind == 1 ? row_bytes_of[1] : kind == 2 ? row_bytes_of[2] : row_bytes_of[3];
     return __ldg(reinterpret_cast<const uint4*>(base + row * rb + off));
   };
   auto put = [&](float* b, const uint4& r, int so, int so2, int kind) {
-    if (kind == 2) { if (A.alpha) *reinterpret_cast<uint4*>(b + so) = r; return; }      // (absent: the kernel forms the decay itself)
+    if (kind == 2) { if (A.alpha || A.head_decay) *reinterpret_cast<uint4*>(b + so) = r; return; }      // (absent: the kernel forms the decay itself)
     float f[VEC];
     if constexpr (sizeof(T) == 2) {
       const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&r);
@@ -449,9 +462,10 @@ extern "C" int qe_linear_attention_scan(const void* q, const void* k, const void
                                         const int* slot_ids, float* out, float q_scale, int R, int max_q_len, int H,
                                         int dk, int dv, int write_state, int dtype, const void* decay_a, long lda,
                                         const void* decay_w, const float* decay_bias, float tau, int rank,
-                                        cudaStream_t stream) {
+                                        const float* head_decay, cudaStream_t stream) {
   if (R <= 0) return 0;
-  if (alpha == nullptr && (decay_a == nullptr || decay_w == nullptr || rank < 1 || !(tau > 0.f) || max_q_len > 1))
+  if (head_decay != nullptr && alpha != nullptr) QE_REFUSE("linear_attention_scan: a decay per head or per channel, not both");
+  if (alpha == nullptr && head_decay == nullptr && (decay_a == nullptr || decay_w == nullptr || rank < 1 || !(tau > 0.f) || max_q_len > 1))
     QE_REFUSE("linear_attention_scan: without alpha, a step of single tokens must bring the decay's inputs");
   if (dk < 1 || dk > 1024 || dv < 1) QE_REFUSE("linear_attention_scan: key size %d must be 1..1024, value size %d positive", dk, dv);
   if (H < 1 || H > 65535) QE_REFUSE("linear_attention_scan: %d heads", H);
@@ -462,7 +476,9 @@ extern "C" int qe_linear_attention_scan(const void* q, const void* k, const void
   A.q = q; A.k = k; A.v = v; A.ldq = ldq; A.ldk = ldk; A.ldv = ldv; A.alpha = alpha; A.state = state;
   A.cu_q = cu_q; A.ctx_lens = ctx_lens; A.slot_ids = slot_ids; A.out = out; A.q_scale = q_scale;
   A.H = H; A.dk = dk; A.dv = dv; A.L = L; A.write_state = write_state;
-  A.da = alpha ? nullptr : decay_a; A.lda = lda; A.dw = decay_w; A.dbias = decay_bias; A.inv_tau = alpha ? 0.f : 1.f / tau; A.R = rank;
+  A.head_decay = head_decay;
+  if (head_decay) decay_a = nullptr;
+  A.da = alpha ? nullptr : decay_a; A.lda = lda; A.dw = decay_w; A.dbias = decay_bias; A.inv_tau = (alpha || head_decay) ? 0.f : 1.f / tau; A.R = rank;
   // a column's threads lie within one warp (L divides 32); a tile of value channels fills up to 256 threads,
   // and is narrower where few requests would leave SMs idle
   int VT = GLA_MAX_COMPUTE / L;

@@ -1,0 +1,235 @@
+// Routed experts: a router that picks `top` of E small feed-forwards per token, and the products over the tokens
+// of each expert.
+//
+//   qe_moe_route       z = W_r h + b in float32 per token; the `top` largest (the lower index wins a tie); weights =
+//                      softmax over the chosen logits alone
+//   qe_moe_sort        the (token, choice) pairs ordered by expert: offsets[E + 1], the pairs of every expert side by
+//                      side, and where each pair went.  One CTA.  Which pair of an expert comes first is not fixed
+//                      (atomics); nothing depends on it, since every pair's row is computed alone
+//   qe_moe_gate_up     act[p, :] = glu(W_gate_e x_t, W_up_e x_t) for the pair p = (t, e) in sorted order
+//   qe_moe_down        y[p, :] = W_down_e act[p, :], float32
+//   qe_moe_combine     out[t, :] = sum over the token's choices, in their order, of weight x y[place of the pair]
+//
+// The grids of the two products are sized for the worst case (every expert's rows end in a tile of their own):
+// nothing of a step's shape depends on the routing, so a step can be replayed from a CUDA graph.
+#include "tile_product.cuh"
+#include <math.h>
+
+#define MOE_MAX_E 1024
+#define MOE_MAX_TOP 32
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const T* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
+                 int* __restrict__ top_idx, float* __restrict__ top_w, int T_tokens, int W, int E, int top) {
+  extern __shared__ float zs[];                     // [warps][E]
+  pdl_launch_dependents();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  const int t = blockIdx.x * warps + warp;
+  if (t >= T_tokens) return;
+  float* z = zs + (size_t)warp * E;
+  const T* xr = x + (size_t)t * W;
+  for (int e = 0; e < E; ++e) {
+    const float* wr = w + (size_t)e * W;
+    float acc = 0.f;
+    for (int d = lane; d < W; d += 32) acc = fmaf(to_f32(xr[d]), wr[d], acc);
+    acc = warp_sum(acc);
+    if (lane == 0) z[e] = acc + (bias ? bias[e] : 0.f);
+  }
+  __syncwarp();
+  float chosen[MOE_MAX_TOP];
+  float zmax = 0.f;
+  for (int j = 0; j < top; ++j) {
+    float best = -INFINITY;
+    int at = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) { const float v = z[e]; if (v > best) { best = v; at = e; } }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+      if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+    }
+    if (at == 0x7fffffff) at = 0;                  // (only logits that are not numbers: the row is lost anyway)
+    chosen[j] = best;
+    if (j == 0) zmax = best;
+    if (lane == 0) { top_idx[(size_t)t * top + j] = at; z[at] = -INFINITY; }
+    __syncwarp();
+  }
+  float sum = 0.f;
+  for (int j = 0; j < top; ++j) { chosen[j] = expf(chosen[j] - zmax); sum += chosen[j]; }
+  if (lane == 0) for (int j = 0; j < top; ++j) top_w[(size_t)t * top + j] = chosen[j] / sum;
+}
+
+extern "C" int qe_moe_route(const void* x, const float* w, const float* bias, int* top_idx, float* top_w, int T, int W,
+                            int E, int top, int dtype, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (E < 1 || E > MOE_MAX_E || top < 1 || top > MOE_MAX_TOP || top > E) QE_REFUSE("moe_route: %d of %d experts", top, E);
+  const int warps = 4;
+  const size_t smem = (size_t)warps * E * sizeof(float);
+#define MR(TT) qe_launch(moe_route_kernel<TT>, dim3((T + warps - 1) / warps), dim3(warps * 32), smem, stream, (const TT*)x, w, bias, \
+                         top_idx, top_w, T, W, E, top)
+  if (dtype == QE_DTYPE_F32) MR(float);
+  else if (dtype == QE_DTYPE_BF16) MR(__nv_bfloat16);
+  else QE_REFUSE("moe_route: unknown dtype %d", dtype);
+#undef MR
+  QE_CHECK_LAUNCH("moe_route");
+  return 0;
+}
+
+__global__ void __launch_bounds__(1024)
+moe_sort_kernel(const int* __restrict__ top_idx, int* __restrict__ offsets, int* __restrict__ sorted_pair,
+                int* __restrict__ place_of_pair, int P, int E) {
+  __shared__ int cnt[MOE_MAX_E + 1];
+  pdl_launch_dependents();
+  pdl_wait();
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < P; p += blockDim.x) atomicAdd(&cnt[top_idx[p]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int e = 0; e < E; ++e) { const int c = cnt[e]; offsets[e] = run; cnt[e] = run; run += c; }
+    offsets[E] = run;
+  }
+  __syncthreads();
+  for (int p = threadIdx.x; p < P; p += blockDim.x) {
+    const int at = atomicAdd(&cnt[top_idx[p]], 1);
+    sorted_pair[at] = p;
+    place_of_pair[p] = at;
+  }
+}
+
+extern "C" int qe_moe_sort(const int* top_idx, int* offsets, int* sorted_pair, int* place_of_pair, int P, int E,
+                           cudaStream_t stream) {
+  if (P <= 0) return 0;
+  if (E < 1 || E > MOE_MAX_E) QE_REFUSE("moe_sort: %d experts", E);
+  qe_launch(moe_sort_kernel, dim3(1), dim3(1024), 0, stream, top_idx, offsets, sorted_pair, place_of_pair, P, E);
+  QE_CHECK_LAUNCH("moe_sort");
+  return 0;
+}
+
+// the expert and the first sorted place of row tile `tile`: experts' tiles are numbered one expert after the other
+__device__ __forceinline__ bool moe_find_tile(const int* __restrict__ offsets, int E, int tile, int* expert, int* first, int* rows) {
+  int seen = 0;
+  for (int e = 0; e < E; ++e) {
+    const int lo = offsets[e], n = offsets[e + 1] - lo;
+    const int tiles = (n + TP_BM - 1) / TP_BM;
+    if (tile < seen + tiles) {
+      const int i = tile - seen;
+      *expert = e; *first = lo + i * TP_BM; *rows = min(TP_BM, n - i * TP_BM);
+      return true;
+    }
+    seen += tiles;
+  }
+  return false;
+}
+
+// GLU = true: w [E, 2 I, K] (gate rows, then up rows), rows gathered from x by pair / top, out [P, I] in the compute type
+// GLU = false: w [E, N, K], rows are x[p], out float32 [P, N]
+template <typename T, bool GLU>
+__global__ void __launch_bounds__(TP_THREADS)
+moe_product_kernel(const T* __restrict__ x, const T* __restrict__ w, const int* __restrict__ offsets,
+                   const int* __restrict__ sorted_pair, void* __restrict__ out_, int E, int N, int K, int top, int act) {
+  __shared__ TpSmem<T, GLU ? 2 : 1> sm;
+  __shared__ int s_tile[4];
+  TpAcc<T, GLU ? 2 : 1> acc;
+  pdl_launch_dependents();
+  pdl_wait();
+  if (threadIdx.x == 0) {
+    int e = 0, first = 0, rows = 0;
+    const bool ok = moe_find_tile(offsets, E, blockIdx.x, &e, &first, &rows);
+    s_tile[0] = ok ? e : -1; s_tile[1] = first; s_tile[2] = rows;
+  }
+  __syncthreads();
+  const int e = s_tile[0], first = s_tile[1], rows = s_tile[2];
+  if (e < 0) return;
+  const int n0 = blockIdx.y * TP_BN;
+  const T* we = w + (size_t)e * (GLU ? 2 : 1) * N * K;
+  tile_product<T, GLU ? 2 : 1>(sm, acc, K,
+      [&](int r) -> const T* {
+        if (r >= rows) return nullptr;
+        return GLU ? x + (size_t)(sorted_pair[first + r] / top) * K : x + (size_t)(first + r) * K;
+      },
+      [&](int m, int n) -> const T* { return n0 + n < N ? we + ((size_t)m * N + n0 + n) * K : nullptr; });
+  tile_for_each<T, GLU ? 2 : 1>(acc, [&](int r, int n, float v0, float v1) {
+    if (r >= rows || n0 + n >= N) return;
+    const size_t at = (size_t)(first + r) * N + n0 + n;
+    if constexpr (GLU) {
+      // gate and up are rounded as if stored, then the activation in float32, rounded once
+      const float g = to_f32(from_f32<T>(v0)), u = to_f32(from_f32<T>(v1));
+      float y;
+      if (act > 1) {
+        const float lim = __int_as_float(act);
+        const float gl = fminf(g, lim), ul = fminf(fmaxf(u, -lim), lim);
+        y = gl / (1.f + expf(-QE_GLU_SIGMOID_SLOPE * gl)) * (ul + 1.f);
+      } else if (act == 1) {
+        y = 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+      } else {
+        y = g / (1.f + expf(-g)) * u;
+      }
+      ((T*)out_)[at] = from_f32<T>(y);
+    } else {
+      ((float*)out_)[at] = v0;
+    }
+  });
+}
+
+static int moe_tiles(int P, int E) { return (P + TP_BM - 1) / TP_BM + (E < P ? E : P); }
+
+extern "C" int qe_moe_gate_up(const void* x, const void* w, const int* offsets, const int* sorted_pair, void* act_out,
+                              int P, int E, int I, int K, int top, int act, int dtype, cudaStream_t stream) {
+  if (P <= 0) return 0;
+  dim3 grid(moe_tiles(P, E), (I + TP_BN - 1) / TP_BN);
+#define MP(TT) qe_launch(moe_product_kernel<TT, true>, grid, dim3(TP_THREADS), 0, stream, (const TT*)x, (const TT*)w, offsets, \
+                         sorted_pair, act_out, E, I, K, top, act)
+  if (dtype == QE_DTYPE_F32) MP(float);
+  else if (dtype == QE_DTYPE_BF16) MP(__nv_bfloat16);
+  else QE_REFUSE("moe_gate_up: unknown dtype %d", dtype);
+#undef MP
+  QE_CHECK_LAUNCH("moe_gate_up");
+  return 0;
+}
+
+extern "C" int qe_moe_down(const void* act_in, const void* w, const int* offsets, float* y, int P, int E, int N, int K,
+                           int dtype, cudaStream_t stream) {
+  if (P <= 0) return 0;
+  dim3 grid(moe_tiles(P, E), (N + TP_BN - 1) / TP_BN);
+#define MP(TT) qe_launch(moe_product_kernel<TT, false>, grid, dim3(TP_THREADS), 0, stream, (const TT*)act_in, (const TT*)w, offsets, \
+                         (const int*)nullptr, (void*)y, E, N, K, 1, 0)
+  if (dtype == QE_DTYPE_F32) MP(float);
+  else if (dtype == QE_DTYPE_BF16) MP(__nv_bfloat16);
+  else QE_REFUSE("moe_down: unknown dtype %d", dtype);
+#undef MP
+  QE_CHECK_LAUNCH("moe_down");
+  return 0;
+}
+
+template <typename T>
+__global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ place_of_pair,
+                                   const float* __restrict__ top_w, T* __restrict__ out, long total, int N, int top) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long e = (long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long)gridDim.x * blockDim.x) {
+    const long t = e / N;
+    const int n = (int)(e - t * N);
+    float acc = 0.f;
+    for (int j = 0; j < top; ++j)
+      acc = fmaf(top_w[t * top + j], y[(size_t)place_of_pair[t * top + j] * N + n], acc);
+    out[e] = from_f32<T>(acc);
+  }
+}
+
+extern "C" int qe_moe_combine(const float* y, const int* place_of_pair, const float* top_w, void* out, int T, int N, int top,
+                              int dtype, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  const long total = (long)T * N;
+  const unsigned blocks = (unsigned)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+#define MC(TT) qe_launch(moe_combine_kernel<TT>, dim3(blocks), dim3(256), 0, stream, y, place_of_pair, top_w, (TT*)out, total, N, top)
+  if (dtype == QE_DTYPE_F32) MC(float);
+  else if (dtype == QE_DTYPE_BF16) MC(__nv_bfloat16);
+  else QE_REFUSE("moe_combine: unknown dtype %d", dtype);
+#undef MC
+  QE_CHECK_LAUNCH("moe_combine");
+  return 0;
+}

@@ -1,0 +1,135 @@
+// A 64 x 64 tile of C = A . B^T by one CTA of 128 threads, for products whose rows are gathered or whose
+// matrices come one per head or per expert, so that they are no plain [M, K] x [N, K] product:
+//
+//   C[r][n] = sum_k A_r[k] * B_n[k]      r < 64 rows given by pointers (null: a row of zeros), n < 64 rows of B
+//
+// float: FFMA, a thread owns 4 rows x 8 columns.  bfloat16: mma.sync m16n8k16 with float32 accumulators, a warp owns
+// 16 rows x 64 columns.  K is walked in steps of 32 through shared memory; the order of a row's sum depends on K
+// alone, so a row's bits do not depend on which other rows share its tile.  NB = 2 runs two B matrices against the
+// same rows (the gate and the up projection of a gated feed-forward).
+#pragma once
+#include "common.cuh"
+
+#define TP_BM 64
+#define TP_BN 64
+#define TP_BK 32
+#define TP_THREADS 128
+
+template <typename T, int NB> struct TpSmem;
+template <int NB> struct alignas(16) TpSmem<float, NB> {
+  float a[TP_BK][TP_BM + 4];
+  float b[NB][TP_BK][TP_BN + 4];
+};
+template <int NB> struct alignas(16) TpSmem<__nv_bfloat16, NB> {
+  __nv_bfloat16 a[TP_BM][TP_BK + 8];
+  __nv_bfloat16 b[NB][TP_BN][TP_BK + 8];
+};
+
+template <typename T, int NB> struct TpAcc;
+template <int NB> struct TpAcc<float, NB> { float v[NB][4][8]; };              // rows ty*4 + i, columns tx*8 + j
+template <int NB> struct TpAcc<__nv_bfloat16, NB> { float v[NB][8][4]; };      // n-tile, mma fragment
+
+__device__ __forceinline__ void tp_mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// a_row(r): pointer to row r's K elements or nullptr; b_row(m, n): pointer to row n of B matrix m or nullptr.
+template <typename T, int NB, typename ARow, typename BRow>
+__device__ __forceinline__ void tile_product(TpSmem<T, NB>& sm, TpAcc<T, NB>& acc, int K, ARow a_row, BRow b_row) {
+  const int tid = threadIdx.x;
+  if constexpr (sizeof(T) == 4) {
+#pragma unroll
+    for (int m = 0; m < NB; ++m)
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc.v[m][i][j] = 0.f;
+  } else {
+#pragma unroll
+    for (int m = 0; m < NB; ++m)
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc.v[m][i][j] = 0.f;
+  }
+  // a thread stages half a row of A and of every B per step: row tid / 2, columns (tid % 2) * 16 ...
+  const int sr = tid >> 1, sc = (tid & 1) * 16;
+  const T* ap = a_row(sr);
+  const T* bp[NB];
+#pragma unroll
+  for (int m = 0; m < NB; ++m) bp[m] = b_row(m, sr);
+  for (int k0 = 0; k0 < K; k0 += TP_BK) {
+    __syncthreads();
+#pragma unroll
+    for (int u = 0; u < 16; ++u) {
+      const int k = k0 + sc + u;
+      const T zero = from_f32<T>(0.f);
+      const T av = (ap && k < K) ? ap[k] : zero;
+      if constexpr (sizeof(T) == 4) sm.a[sc + u][sr] = av; else sm.a[sr][sc + u] = av;
+#pragma unroll
+      for (int m = 0; m < NB; ++m) {
+        const T bv = (bp[m] && k < K) ? bp[m][k] : zero;
+        if constexpr (sizeof(T) == 4) sm.b[m][sc + u][sr] = bv; else sm.b[m][sr][sc + u] = bv;
+      }
+    }
+    __syncthreads();
+    if constexpr (sizeof(T) == 4) {
+      const int ty = tid >> 3, tx = tid & 7;
+#pragma unroll 8
+      for (int k = 0; k < TP_BK; ++k) {
+        const float4 a4 = *reinterpret_cast<const float4*>(&sm.a[k][ty * 4]);
+        const float av[4] = {a4.x, a4.y, a4.z, a4.w};
+#pragma unroll
+        for (int m = 0; m < NB; ++m) {
+          const float4 b0 = *reinterpret_cast<const float4*>(&sm.b[m][k][tx * 8]);
+          const float4 b1 = *reinterpret_cast<const float4*>(&sm.b[m][k][tx * 8 + 4]);
+          const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc.v[m][i][j] = fmaf(av[i], bv[j], acc.v[m][i][j]);
+        }
+      }
+    } else {
+      const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
+#pragma unroll
+      for (int kk = 0; kk < TP_BK; kk += 16) {
+        uint32_t a[4];
+        a[0] = *reinterpret_cast<const uint32_t*>(&sm.a[warp * 16 + g][kk + 2 * c]);
+        a[1] = *reinterpret_cast<const uint32_t*>(&sm.a[warp * 16 + g + 8][kk + 2 * c]);
+        a[2] = *reinterpret_cast<const uint32_t*>(&sm.a[warp * 16 + g][kk + 2 * c + 8]);
+        a[3] = *reinterpret_cast<const uint32_t*>(&sm.a[warp * 16 + g + 8][kk + 2 * c + 8]);
+#pragma unroll
+        for (int m = 0; m < NB; ++m)
+#pragma unroll
+          for (int nt = 0; nt < 8; ++nt) {
+            const uint32_t b0 = *reinterpret_cast<const uint32_t*>(&sm.b[m][nt * 8 + g][kk + 2 * c]);
+            const uint32_t b1 = *reinterpret_cast<const uint32_t*>(&sm.b[m][nt * 8 + g][kk + 2 * c + 8]);
+            tp_mma_bf16(acc.v[m][nt], a, b0, b1);
+          }
+      }
+    }
+  }
+}
+
+// Every element of the tile that the thread holds: f(row in tile, column in tile, value of B matrix 0[, of 1]).
+template <typename T, int NB, typename F>
+__device__ __forceinline__ void tile_for_each(const TpAcc<T, NB>& acc, F f) {
+  const int tid = threadIdx.x;
+  if constexpr (sizeof(T) == 4) {
+    const int ty = tid >> 3, tx = tid & 7;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f(ty * 4 + i, tx * 8 + j, acc.v[0][i][j], NB > 1 ? acc.v[NB - 1][i][j] : 0.f);
+  } else {
+    const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        f(warp * 16 + g + (e >> 1) * 8, nt * 8 + 2 * c + (e & 1), acc.v[0][nt][e], NB > 1 ? acc.v[NB - 1][nt][e] : 0.f);
+  }
+}

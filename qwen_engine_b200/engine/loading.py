@@ -39,7 +39,7 @@ def pages_for_memory_fraction(model: DecoderModel, page_size: int, dtype: torch.
     free, total = torch.cuda.mem_get_info(torch.device(device))
     budget = int(total * fraction) - (total - free) - reserve_bytes
     specs = [s for s in model.cache_specs() if s is not None and hasattr(s, "num_kv_heads")]
-    per_page = sum(2 * s.num_kv_heads * page_size * s.head_dim * dtype.itemsize for s in specs)
+    per_page = sum(getattr(s, "planes", 2) * s.num_kv_heads * page_size * s.head_dim * dtype.itemsize for s in specs)
     if per_page == 0:
         return 1
     pages = budget // per_page

@@ -65,6 +65,8 @@ class ModelLayout:
     tie_head: bool = True
     max_positions: Optional[int] = None
     embed_scale: float = 1.0    # the embedding output is the table's row times this (the head uses the table as it is)
+    embed_norm: Optional[PartSpec] = None         # a norm that the embedding output passes before the first layer ...
+    embed_norm_prefix: str = "embed.norm"         # ... and the prefix of its tensors
 
 
 class DecoderModel:
@@ -72,6 +74,7 @@ class DecoderModel:
         self.layout = layout
         self.blocks: list[Block] = [ls.block.build("block") for ls in layout.layers]
         self.final_norm = layout.final_norm.build("norm")
+        self.embed_norm = layout.embed_norm.build("norm") if layout.embed_norm is not None else None
         self.embed: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
         self.dtype: Optional[torch.dtype] = None
@@ -111,6 +114,8 @@ class DecoderModel:
     def weight_manifest(self) -> list[WeightSpec]:
         lo = self.layout
         specs = [WeightSpec(lo.embed_name, (lo.vocab_size, lo.hidden_size), MATRIX)]
+        if self.embed_norm is not None:
+            specs += self.embed_norm.weight_specs(lo.embed_norm_prefix)
         for ls, block in zip(lo.layers, self.blocks):
             specs += block.weight_specs(ls.weight_prefix)
         specs += self.final_norm.weight_specs(lo.final_norm_prefix)
@@ -129,6 +134,8 @@ class DecoderModel:
         for ls, block in zip(lo.layers, self.blocks):
             block.load(ls.weight_prefix, source, dtype, device)
         self.final_norm.load(lo.final_norm_prefix, source, dtype, device)
+        if self.embed_norm is not None:
+            self.embed_norm.load(lo.embed_norm_prefix, source, dtype, device)
         if lo.tie_head:
             self.head = self.embed            # the same storage (model.py:417-418)
             if lo.head_name is not None and lo.head_name in set(source.names()):
@@ -161,6 +168,8 @@ class DecoderModel:
         for b in self.blocks:
             visit(b)
         visit(self.final_norm)
+        if self.embed_norm is not None:
+            visit(self.embed_norm)
         return total
 
     # ---- one step ---------------------------------------------------------------------
@@ -170,7 +179,14 @@ class DecoderModel:
         lo = self.layout
         T, H = ctx.num_tokens, lo.hidden_size
         stream = ops.ResidualStream.for_step(ctx.arena.alloc, T, H, ctx.dtype)
-        ops.embedding(ctx.token_ids, self.embed, stream, scale=lo.embed_scale)
+        if self.embed_norm is None:
+            ops.embedding(ctx.token_ids, self.embed, stream, scale=lo.embed_scale)
+        else:
+            # the table's rows, normed in float32, are what the stream starts from
+            rows = ctx.arena.alloc((T, H), torch.float32)
+            ops.embedding(ctx.token_ids, self.embed, rows, scale=lo.embed_scale)
+            self.embed_norm.add_norm(ctx, rows, None, stream.resid)
+            stream.has_delta, stream.n_ssq = False, 0
         views = []
         for e in lo.plan:
             if not e.slots:

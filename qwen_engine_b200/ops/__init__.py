@@ -64,6 +64,27 @@ TC_FORCE_CAP = -1       # the most key steps of a work item (0: cut nothing); be
 
 
 GATE_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}     # the functions a gated feed-forward may put on its gate
+LIMITED_GLU = "swish_limit"    # ("swish_limit", L): g' = min(g, L), u' = clamp(u, -L, L), g' sigmoid(1.702 g') (u' + 1)
+
+
+def gate_activation_known(activation) -> bool:
+    if isinstance(activation, (tuple, list)):
+        return len(activation) == 2 and activation[0] == LIMITED_GLU and float(activation[1]) > 0.0
+    return activation in GATE_ACTIVATIONS
+
+
+def gate_code(activation) -> int:
+    """The number the kernels take for a gated feed-forward's form: 0 silu, 1 the tanh form of gelu, and for the
+    limited form the bit pattern of its float32 limit (every positive float's pattern is an integer above 1)."""
+    if not gate_activation_known(activation):
+        raise KernelRefused(f"unknown activation {activation!r}; known: {sorted(GATE_ACTIVATIONS)} and ({LIMITED_GLU!r}, limit)")
+    if isinstance(activation, (tuple, list)):
+        import struct
+        code = struct.unpack("<i", struct.pack("<f", float(activation[1])))[0]
+        if code <= 1:
+            raise KernelRefused(f"the limit {activation[1]!r} of a limited feed-forward is too small")
+        return code
+    return GATE_ACTIVATIONS[activation]
 
 
 class ExtensionMissing(RuntimeError):
@@ -492,7 +513,7 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, a
     _need(out.shape == (M, I) and out.dtype in (torch.bfloat16, torch.float32), "linear_swiglu: out must be [M, I]")
     _need(x.is_contiguous() and w_gate_up.is_contiguous() and out.is_contiguous(), "linear_swiglu: operands must be contiguous")
     _check(lib().qe_linear_swiglu_tcgen05_pair(_ptr(x), _ptr(w_gate_up), _ptr(out), M, I, K,
-                                               int(out.dtype == torch.float32), GATE_ACTIVATIONS[activation], _stream()), "linear_swiglu")
+                                               int(out.dtype == torch.float32), gate_code(activation), _stream()), "linear_swiglu")
 
 
 SWIGLU_SMALL_MAX_M = 16     # rows up to which the weight-streaming product forms the activation in its epilogue
@@ -517,7 +538,7 @@ def linear_swiglu_small(x, w_gate_up: torch.Tensor, out: torch.Tensor, activatio
           f"linear_swiglu_small: out must be bfloat16 [M, I] with M <= {SWIGLU_SMALL_MAX_M}")
     _need(x.is_contiguous() and w_gate_up.is_contiguous() and out.is_contiguous(), "linear_swiglu_small: operands must be contiguous")
     _hand_over_next_weights()
-    _check(lib().qe_linear_small_m_swiglu(_ptr(x), _ptr(w_gate_up), _ptr(out), M, I, K, GATE_ACTIVATIONS[activation], _stream()),
+    _check(lib().qe_linear_small_m_swiglu(_ptr(x), _ptr(w_gate_up), _ptr(out), M, I, K, gate_code(activation), _stream()),
            "linear_swiglu_small")
 
 
@@ -896,6 +917,12 @@ def split_geometry(geo) -> tuple:
     return Hq, Hkv, D, window, bool(len(geo) > 4 and geo[4])
 
 
+def geometry_planes(geo) -> int:
+    """The sixth entry of a geometry, if it has one: 1 for a cache whose pages hold one plane per kv head, the values
+    being the keys' channels (a latent cache; the tcgen05 kernel does not take it), else 2."""
+    return int(geo[5]) if len(geo) > 5 else 2
+
+
 def plan_attention(q_lens: list[int], ctx_lens: list[int], page_size: int,
                    geometries=(), dtype: torch.dtype = torch.float32,
                    uniform_splits: Optional[dict] = None) -> dict[str, list[int]]:
@@ -922,7 +949,7 @@ def plan_attention(q_lens: list[int], ctx_lens: list[int], page_size: int,
             continue
         G = Hq // Hkv
         tpt = FLASH_ROWS // G
-        use_tc = uniform_splits is None and tc_attention_supported(dtype, Hq, Hkv, D, page_size)
+        use_tc = uniform_splits is None and geometry_planes(geo) == 2 and tc_attention_supported(dtype, Hq, Hkv, D, page_size)
         on_tc = [use_tc and n * G >= TC_MIN_ROWS for n in q_lens]
         tc_tiles: list = []
         base = sum(-(-n // tpt) for n, tc in zip(q_lens, on_tc) if not tc) * Hkv
@@ -1052,15 +1079,20 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
     Hq, Hkv, D = num_heads, num_kv_heads, head_dim
     T = qkv.shape[0]
     _need(out.shape == (T, Hq * D) and out.is_contiguous() and out.dtype == qkv.dtype, "paged_attention: out must be [T, Hq D]")
-    _need(kv_pages.dtype == qkv.dtype and kv_pages.dim() == 5 and kv_pages.is_contiguous(),
-          "paged_attention: kv_pages must be [pages, 2, Hkv, page, D] in q's dtype")
+    _need(kv_pages.dtype == qkv.dtype and kv_pages.dim() == 5 and kv_pages.is_contiguous() and kv_pages.shape[1] in (1, 2),
+          "paged_attention: kv_pages must be [pages, 2 (or 1: the values are the keys' channels), Hkv, page, D] in q's dtype")
+    planes = int(kv_pages.shape[1])
     _i32(block_tables, "block_tables")
     global last_attention_kernel
     plan = ctx.attn_plan
     if slopes is not None:
         _need(slopes.dtype == torch.float32 and slopes.numel() == Hq and slopes.is_contiguous(), "paged_attention: slopes must be float32 [Hq]")
     index = plan.get("geometry_index", {})
-    key = index.get((Hq, Hkv, D, window, True)) if slopes is not None else index.get((Hq, Hkv, D, window), index.get((Hq, Hkv, D, window, False)))
+    if planes == 1:
+        _need(slopes is None, "paged_attention: no distance bias over a cache of one plane")
+        key = index.get((Hq, Hkv, D, window, False, 1))
+    else:
+        key = index.get((Hq, Hkv, D, window, True)) if slopes is not None else index.get((Hq, Hkv, D, window), index.get((Hq, Hkv, D, window, False)))
     if key is not None and f"tc{key}_items" in plan:
         last_attention_kernel = "flash_attention_tc"
         tc_items = plan[f"tc{key}_items"]
@@ -1105,7 +1137,7 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
                 _ptr(qkv), ctypes.c_long(qkv.stride(0)), _ptr(kv_pages), _ptr(ahead), _ptr(block_tables), int(block_tables.shape[1]),
                 _ptr(items), n_items, _ptr(out), _ptr(part_acc), _ptr(part_ml), int(part_rows), _ptr(counters),
                 int(max_rows), cluster, int(DECODE_ATTENTION_MMA_WIDE and n_items * Hkv <= TC_TARGET_CTAS),
-                ctypes.c_float(scale), int(window), Hq, Hkv, D, int(kv_pages.shape[3]), _ptr(slopes), _stream()),
+                ctypes.c_float(scale), int(window), Hq, Hkv, D, int(kv_pages.shape[3]), _ptr(slopes), planes, _stream()),
                 "decode_attention_mma")
             return
         last_attention_kernel = "flash_attention"
@@ -1113,7 +1145,7 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
             _ptr(qkv), ctypes.c_long(qkv.stride(0)), _ptr(kv_pages), _ptr(block_tables), int(block_tables.shape[1]),
             _ptr(ctx.cu_q), _ptr(ctx.ctx_lens), _ptr(items), n_items, _ptr(merge), n_merge, _ptr(out),
             _ptr(part_acc), _ptr(part_ml), int(part_rows), _ptr(counters), int(small_tiles), ctypes.c_float(scale), int(window),
-            Hq, Hkv, D, int(kv_pages.shape[3]), _ptr(slopes), _stream()), "flash_attention")
+            Hq, Hkv, D, int(kv_pages.shape[3]), _ptr(slopes), planes, _stream()), "flash_attention")
         return
     tiles = plan["tiles"]
     n_tiles = tiles.numel() // 2
@@ -1121,7 +1153,7 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
     _check(lib().qe_paged_attention_generic(
         _ptr(qkv), ctypes.c_long(qkv.stride(0)), _ptr(kv_pages), _ptr(block_tables), int(block_tables.shape[1]),
         _ptr(ctx.cu_q), _ptr(ctx.ctx_lens), _ptr(tiles), n_tiles, _ptr(out), ctypes.c_float(scale), int(window),
-        Hq, Hkv, D, int(kv_pages.shape[3]), _dt(qkv), _ptr(slopes), _stream()), "paged_attention")
+        Hq, Hkv, D, int(kv_pages.shape[3]), _dt(qkv), _ptr(slopes), planes, _stream()), "paged_attention")
 
 
 def place_tokens(token_ids: torch.Tensor, rows: torch.Tensor, src: torch.Tensor, src_index: torch.Tensor) -> None:
@@ -1157,19 +1189,21 @@ def act_mul(gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu") 
     """out[t, i] = act(gate_up[t, i]) * gate_up[t, I + i]; act "silu", or "gelu_tanh":
     0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).  Float32 arithmetic, rounded once."""
     T, I2 = gate_up.shape
-    _need(activation in GATE_ACTIVATIONS, f"act_mul: unknown activation {activation!r}")
+    _need(gate_activation_known(activation), f"act_mul: unknown activation {activation!r}")
     _need(I2 % 2 == 0 and out.shape == (T, I2 // 2) and out.dtype == gate_up.dtype
           and out.is_contiguous() and gate_up.is_contiguous(), "act_mul: out must be [T, I] for gate_up [T, 2I]")
-    _check(lib().qe_act_mul(_ptr(gate_up), _ptr(out), T, I2 // 2, _dt(out), GATE_ACTIVATIONS[activation], _stream()), "act_mul")
+    _check(lib().qe_act_mul(_ptr(gate_up), _ptr(out), T, I2 // 2, _dt(out), gate_code(activation), _stream()), "act_mul")
 
 
 def _rows(t: torch.Tensor, name: str) -> None:
     _need(t.dim() == 2 and t.stride(1) == 1, f"{name} must be rows with unit stride along the columns")
 
 
-def channel_decay(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], tau: float, out: torch.Tensor) -> None:
+def channel_decay(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], tau: float, out: torch.Tensor,
+                  log_rate: Optional[torch.Tensor] = None) -> None:
     """out[t, n] = sigmoid(z)^(1 / tau) with z = a[t] . w[n] + bias[n], in float32: the decay of a recurrence
-    from the second half of a low-rank pair.  a [T, R] (rows may be strided), w [N, R], out float32 [T, N]."""
+    from the second half of a low-rank pair.  a [T, R] (rows may be strided), w [N, R], out float32 [T, N].
+    With ``log_rate`` (float32 [G], G dividing N): out = exp(-exp(log_rate[n // (N / G)]) softplus(z)) instead."""
     _rows(a, "channel_decay: a")
     T, R = a.shape
     N = w.shape[0]
@@ -1177,8 +1211,13 @@ def channel_decay(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]
     _need(out.shape == (T, N) and out.dtype == torch.float32 and out.is_contiguous(), "channel_decay: out must be float32 [T, N]")
     if bias is not None:
         _need(bias.dtype == torch.float32 and bias.shape == (N,) and bias.is_contiguous(), "channel_decay: bias must be float32 [N]")
+    per = 1
+    if log_rate is not None:
+        _need(log_rate.dtype == torch.float32 and log_rate.dim() == 1 and log_rate.is_contiguous() and N % log_rate.numel() == 0,
+              "channel_decay: log_rate must be float32 [G] with G dividing N")
+        per = N // log_rate.numel()
     _check(lib().qe_channel_decay(_ptr(a), ctypes.c_long(a.stride(0)), _ptr(w), _ptr(bias), ctypes.c_float(tau), _ptr(out),
-                                  T, N, R, _dt(a), _stream()), "channel_decay")
+                                  T, N, R, _dt(a), _ptr(log_rate), per, _stream()), "channel_decay")
 
 
 SCAN_FORMS_DECAY = True     # steps of single tokens: the scan forms the decay from the low-rank pair itself (no decay kernel)
@@ -1186,13 +1225,14 @@ SCAN_FORMS_DECAY = True     # steps of single tokens: the scan forms the decay f
 
 def linear_attention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, alpha: Optional[torch.Tensor], state: torch.Tensor,
                           ctx, out: torch.Tensor, q_scale: float, num_heads: int, key_dim: int, value_dim: int,
-                          write_state: bool = True, decay=None) -> None:
+                          write_state: bool = True, decay=None, head_decay: Optional[torch.Tensor] = None) -> None:
     """The recurrence S <- diag(alpha_t) S + k_t v_t^T, o_t = S^T (q_scale q_t) per head, over the step's
     tokens of every request, from the state its slot holds (zero for a request without context) to the
     state after its last token.  q, k [T, H dk] and v [T, H dv] in the compute type (rows may be strided),
     alpha float32 [T, H dk], state float32 [slots, H, dv, dk], out float32 [T, H dv].
     A step of single tokens may leave ``alpha`` None and give ``decay`` = (a, w, bias, tau) as ``channel_decay``
-    takes them: the scan then forms alpha itself, to the same bits."""
+    takes them: the scan then forms alpha itself, to the same bits.  ``head_decay`` (float32 [H]) in the place of
+    both: alpha is one constant per head."""
     H, dk, dv = num_heads, key_dim, value_dim
     T = q.shape[0]
     for t, name, width in ((q, "q", H * dk), (k, "k", H * dk), (v, "v", H * dv)):
@@ -1200,7 +1240,10 @@ def linear_attention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, alp
         _need(t.shape == (T, width) and t.dtype == q.dtype, f"linear_attention_scan: {name} must be [T, {width}]")
     da = dw = db = None
     tau, rank = 1.0, 0
-    if alpha is None:
+    if head_decay is not None:
+        _need(alpha is None and decay is None and head_decay.dtype == torch.float32 and head_decay.shape == (H,)
+              and head_decay.is_contiguous(), "linear_attention_scan: head_decay must be float32 [H], alone")
+    elif alpha is None:
         _need(decay is not None and int(ctx.max_q_len) <= 1, "linear_attention_scan: without alpha, single tokens and the decay's inputs")
         da, dw, db, tau = decay
         _rows(da, "linear_attention_scan: decay a")
@@ -1220,7 +1263,8 @@ def linear_attention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, alp
         _ptr(q), _ptr(k), _ptr(v), ctypes.c_long(q.stride(0)), ctypes.c_long(k.stride(0)), ctypes.c_long(v.stride(0)),
         _ptr(alpha), _ptr(state), _ptr(ctx.cu_q), _ptr(ctx.ctx_lens), _ptr(ctx.slot_ids), _ptr(out), ctypes.c_float(q_scale),
         int(ctx.num_reqs), int(ctx.max_q_len), H, dk, dv, int(bool(write_state)), _dt(q), _ptr(da),
-        ctypes.c_long(da.stride(0) if da is not None else 0), _ptr(dw), _ptr(db), ctypes.c_float(tau), int(rank), _stream()),
+        ctypes.c_long(da.stride(0) if da is not None else 0), _ptr(dw), _ptr(db), ctypes.c_float(tau), int(rank),
+        _ptr(head_decay), _stream()),
         "linear_attention_scan")
 
 
@@ -1250,6 +1294,140 @@ def head_norm_gate(x: torch.Tensor, gate: Optional[torch.Tensor], weight: Option
         ctypes.c_long(gate.stride(0) if gate is not None else 0), _ptr(weight), ctypes.c_float(eps), _ptr(out),
         ctypes.c_long(out.stride(0)), ctypes.c_float(scale), _GATES[gate_kind if gate is not None else None], T, H, D, _dt(out),
         _stream()), "head_norm_gate")
+
+
+def latent_prepare(down: torch.Tensor, q: torch.Tensor, norm_w: torch.Tensor, eps: float, positions: torch.Tensor,
+                   inv_freq: torch.Tensor, rot_dims: int, cache: torch.Tensor, slot_mapping: torch.Tensor,
+                   qlat: torch.Tensor, num_heads: int, plain_dim: int, latent_dim: int, rot_dim: int,
+                   write_kv: bool = True) -> None:
+    """What latent attention does per token before the attention kernel.  ``down`` [T, R + Dr] (rows may be strided): the
+    first R channels are RMS-normed (weight ``norm_w``) into the token's cache row, the last Dr are the key part all
+    heads share, whose first ``rot_dims`` channels turn (pairs (i, i + rot_dims / 2), angle position x inv_freq[i]) on
+    their way into the cache row's tail.  ``q`` [T, H (dn + Dr)]: every head's last Dr channels turn likewise into
+    ``qlat`` [T, H, R + Dr] behind the room for the head's folded plain part.  cache [pages, 1, 1, page, R + Dr]."""
+    _rows(down, "latent_prepare: down")
+    _rows(q, "latent_prepare: q")
+    T = q.shape[0]
+    H, dn, R, Dr = num_heads, plain_dim, latent_dim, rot_dim
+    _need(down.shape == (T, R + Dr) and q.shape == (T, H * (dn + Dr)) and down.dtype == q.dtype == qlat.dtype == cache.dtype,
+          "latent_prepare: down [T, R + Dr], q [T, H (dn + Dr)] in the cache's dtype")
+    _need(qlat.shape == (T, H * (R + Dr)) and qlat.is_contiguous(), "latent_prepare: qlat must be [T, H (R + Dr)]")
+    _need(cache.dim() == 5 and cache.shape[1] == 1 and cache.shape[2] == 1 and cache.shape[4] == R + Dr and cache.is_contiguous(),
+          "latent_prepare: cache must be [pages, 1, 1, page, R + Dr]")
+    _need(norm_w.dtype == torch.float32 and norm_w.shape == (R,) and inv_freq.dtype == torch.float32
+          and inv_freq.numel() >= rot_dims // 2, "latent_prepare: float32 norm weight [R] and inv_freq [rot_dims / 2]")
+    _i32(positions, "positions")
+    _i32(slot_mapping, "slot_mapping")
+    _check(lib().qe_latent_prepare(_ptr(down), ctypes.c_long(down.stride(0)), _ptr(q), ctypes.c_long(q.stride(0)), _ptr(norm_w),
+                                   ctypes.c_float(eps), _ptr(positions), _ptr(inv_freq), int(rot_dims), _ptr(cache),
+                                   _ptr(slot_mapping), _ptr(qlat), T, H, dn, R, Dr, int(bool(write_kv)), _dt(q), _stream()),
+           "latent_prepare")
+
+
+def head_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, x_head_stride: int, out_head_stride: int) -> None:
+    """out[t, h * out_head_stride + n] = sum_k w[h, n, k] x[t, h * x_head_stride + k]: one matrix per head, w [H, N, K];
+    x and out are rows (unit stride along columns) in w's dtype, float32 accumulation."""
+    _rows(x, "head_linear: x")
+    _rows(out, "head_linear: out")
+    H, N, K = w.shape
+    M = x.shape[0]
+    _need(w.is_contiguous() and x.dtype == w.dtype == out.dtype and out.shape[0] == M, "head_linear: operands of one dtype, w contiguous")
+    _need((H - 1) * x_head_stride + K <= x.shape[1] and (H - 1) * out_head_stride + N <= out.shape[1],
+          "head_linear: the heads do not fit the rows")
+    _check(lib().qe_head_linear(_ptr(x), ctypes.c_long(x.stride(0)), ctypes.c_long(x_head_stride), _ptr(w), _ptr(out),
+                                ctypes.c_long(out.stride(0)), ctypes.c_long(out_head_stride), M, H, N, K, _dt(x), _stream()),
+           "head_linear")
+
+
+def short_conv(x: torch.Tensor, w: torch.Tensor, state: torch.Tensor, ctx, out: torch.Tensor, write_state: bool = True,
+               silu: bool = True) -> None:
+    """A short causal convolution over the tokens of each request, channel by channel, then silu:
+    out[t, c] = silu(sum_j w[c, j] x[t - (taps - 1) + j, c]).  x [T, C] in the compute type (rows may be strided);
+    w float32 [C, taps], the last column is the current token's; state float32 [slots, taps - 1, C] holds each
+    request's last taps - 1 inputs (zeros count for a request without context) and is moved on; out float32 [T, C]."""
+    _rows(x, "short_conv: x")
+    T, C = x.shape
+    taps = w.shape[1]
+    _need(w.shape == (C, taps) and w.dtype == torch.float32 and w.is_contiguous(), "short_conv: w must be float32 [C, taps]")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (taps - 1, C),
+          "short_conv: state must be float32 [slots, taps - 1, C]")
+    _need(out.shape == (T, C) and out.dtype == torch.float32 and out.is_contiguous(), "short_conv: out must be float32 [T, C]")
+    _check(lib().qe_short_conv(_ptr(x), ctypes.c_long(x.stride(0)), _ptr(w), _ptr(state), _ptr(ctx.cu_q), _ptr(ctx.ctx_lens),
+                               _ptr(ctx.slot_ids), _ptr(out), int(ctx.num_reqs), int(ctx.max_q_len), C, taps,
+                               int(bool(write_state)), int(bool(silu)), _dt(x), _stream()), "short_conv")
+
+
+def unit_norm(x: torch.Tensor, num_heads: int, head_dim: int, eps: float, scale: float = 1.0) -> None:
+    """x[t, h] <- x[t, h] / sqrt(sum x[t, h]^2 + eps) * scale in place; x float32 [T, H D] (rows may be strided)."""
+    _rows(x, "unit_norm: x")
+    _need(x.dtype == torch.float32 and x.shape[1] == num_heads * head_dim, "unit_norm: x must be float32 [T, H D]")
+    _check(lib().qe_unit_norm(_ptr(x), ctypes.c_long(x.stride(0)), int(x.shape[0]), num_heads, head_dim, ctypes.c_float(eps),
+                              ctypes.c_float(scale), _stream()), "unit_norm")
+
+
+def delta_rule_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: Optional[torch.Tensor], beta: Optional[torch.Tensor],
+                    state: torch.Tensor, ctx, out: torch.Tensor, num_heads: int, num_key_heads: int, key_dim: int,
+                    value_dim: int, write_state: bool = True) -> None:
+    """The gated delta rule per head over the step's tokens of every request, from the state its slot holds:
+    S <- diag(g_t) S; u = sigmoid(beta_t) (v_t - S^T k_t); S <- S + k_t u^T; o_t = S^T q_t.
+    q, k float32 [T, G dk] (head h reads group h // (H / G)), v float32 [T, H dv], g float32 [T, H dk] (None: no
+    decay), beta [T, H] before its sigmoid in the compute type (rows may be strided), state float32
+    [slots, H, dv, dk], out float32 [T, H dv].  Rows of q, k, v and g may be strided."""
+    H, G, dk, dv = num_heads, num_key_heads, key_dim, value_dim
+    T = q.shape[0]
+    for t, name, width in ((q, "q", G * dk), (k, "k", G * dk), (v, "v", H * dv)) + (((g, "g", H * dk),) if g is not None else ()):
+        _rows(t, f"delta_rule_scan: {name}")
+        _need(t.shape == (T, width) and t.dtype == torch.float32, f"delta_rule_scan: {name} must be float32 [T, {width}]")
+    _rows(beta, "delta_rule_scan: beta")
+    _need(beta.shape == (T, H), "delta_rule_scan: beta must be [T, H]")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (H, dv, dk),
+          "delta_rule_scan: state must be float32 [slots, H, dv, dk]")
+    _need(out.shape == (T, H * dv) and out.dtype == torch.float32 and out.is_contiguous(), "delta_rule_scan: out must be float32 [T, H dv]")
+    _check(lib().qe_delta_rule_scan(_ptr(q), ctypes.c_long(q.stride(0)), _ptr(k), ctypes.c_long(k.stride(0)), _ptr(v),
+                                    ctypes.c_long(v.stride(0)), _ptr(g), ctypes.c_long(g.stride(0) if g is not None else 0),
+                                    _ptr(beta), ctypes.c_long(beta.stride(0)), _dt(beta),
+                                    ctypes.c_void_p(0), _ptr(state), _ptr(ctx.cu_q), _ptr(ctx.ctx_lens), _ptr(ctx.slot_ids),
+                                    _ptr(out), int(ctx.num_reqs), H, G, dk, dv, int(bool(write_state)), 1, _stream()),
+           "delta_rule_scan")
+
+
+def moe_route(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], top_idx: torch.Tensor, top_w: torch.Tensor) -> None:
+    """Router of routed experts: z = w x[t] + bias in float32 (x in the compute type, w float32 [E, W]); the ``top``
+    largest logits' experts into top_idx int32 [T, top] (the lower index wins a tie) and the softmax over those
+    logits alone into top_w float32 [T, top]."""
+    T, W = x.shape
+    E = w.shape[0]
+    top = top_idx.shape[1]
+    _need(x.is_contiguous() and w.dtype == torch.float32 and w.shape == (E, W) and w.is_contiguous(), "moe_route: w must be float32 [E, W]")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.shape == (E,)), "moe_route: bias must be float32 [E]")
+    _need(top_idx.shape == (T, top) and top_idx.dtype == torch.int32 and top_idx.is_contiguous()
+          and top_w.shape == (T, top) and top_w.dtype == torch.float32 and top_w.is_contiguous(), "moe_route: outputs [T, top]")
+    _check(lib().qe_moe_route(_ptr(x), _ptr(w), _ptr(bias), _ptr(top_idx), _ptr(top_w), T, W, E, top, _dt(x), _stream()), "moe_route")
+
+
+def moe_experts(x: torch.Tensor, top_idx: torch.Tensor, top_w: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor,
+                out: torch.Tensor, activation, alloc) -> None:
+    """out[t] = sum_j top_w[t, j] * W_down[e] glu(W_gate[e] x[t], W_up[e] x[t]) with e = top_idx[t, j]: the pairs are
+    ordered by expert on the device, each expert's rows run as tiles of two grouped products, and the token's choices
+    are summed in their order.  w_gate_up [E, 2 I, K] (gate rows, then up rows), w_down [E, N, I]; ``alloc(shape,
+    dtype)`` gives scratch memory.  Nothing of the launches depends on the routing."""
+    T, K = x.shape
+    E, I2, _ = w_gate_up.shape
+    I, N, top = I2 // 2, w_down.shape[1], top_idx.shape[1]
+    P = T * top
+    _need(x.is_contiguous() and w_gate_up.is_contiguous() and w_down.is_contiguous() and w_gate_up.shape == (E, 2 * I, K)
+          and w_down.shape == (E, N, I) and x.dtype == w_gate_up.dtype == w_down.dtype, "moe_experts: w_gate_up [E, 2 I, K], w_down [E, N, I] in x's dtype")
+    _need(out.shape == (T, N) and out.is_contiguous(), "moe_experts: out must be [T, N]")
+    offsets = alloc((E + 1,), torch.int32)
+    sorted_pair = alloc((P,), torch.int32)
+    place = alloc((P,), torch.int32)
+    _check(lib().qe_moe_sort(_ptr(top_idx), _ptr(offsets), _ptr(sorted_pair), _ptr(place), P, E, _stream()), "moe_sort")
+    act = alloc((P, I), x.dtype)
+    _check(lib().qe_moe_gate_up(_ptr(x), _ptr(w_gate_up), _ptr(offsets), _ptr(sorted_pair), _ptr(act), P, E, I, K, top,
+                                gate_code(activation), _dt(x), _stream()), "moe_gate_up")
+    y = alloc((P, N), torch.float32)
+    _check(lib().qe_moe_down(_ptr(act), _ptr(w_down), _ptr(offsets), _ptr(y), P, E, N, I, _dt(x), _stream()), "moe_down")
+    _check(lib().qe_moe_combine(_ptr(y), _ptr(place), _ptr(top_w), _ptr(out), T, N, top, _dt(out), _stream()), "moe_combine")
 
 
 def scaled_add(acc: torch.Tensor, x: torch.Tensor, scale: float, first: bool = False) -> None:

@@ -4,12 +4,15 @@ from .base import (Arena, Block, FeedForward, GroupStepView, Mixer, Norm, Part, 
 from .norm import RMSNorm
 from .rope import NeoxRope
 from .attention import GQAAttention
-from .linear_attention import GatedLinearAttention
+from .linear_attention import DecayedLinearAttention, GatedLinearAttention
+from .latent_attention import LatentAttention
+from .delta_rule import GatedDeltaRule
+from .moe import RoutedExperts
 from .parallel import ParallelMixers
 from .mlp import SwiGLU
 from .block import PreNormBlock
 
 __all__ = ["Arena", "Block", "FeedForward", "GroupStepView", "Mixer", "Norm", "Part", "PartSpec",
            "PositionEncoding", "StepContext", "register", "NORMS", "POSITION_ENCODINGS", "MIXERS",
-           "FEED_FORWARDS", "BLOCKS", "RMSNorm", "NeoxRope", "GQAAttention", "GatedLinearAttention", "ParallelMixers", "SwiGLU",
+           "FEED_FORWARDS", "BLOCKS", "RMSNorm", "NeoxRope", "GQAAttention", "GatedLinearAttention", "DecayedLinearAttention", "LatentAttention", "GatedDeltaRule", "RoutedExperts", "ParallelMixers", "SwiGLU",
            "PreNormBlock"]

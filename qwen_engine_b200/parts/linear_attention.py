@@ -130,3 +130,78 @@ class GatedLinearAttention(Mixer):
         inner = ctx.arena.alloc((ctx.num_tokens, self.inner_width), ctx.dtype)
         self.mix_into(ctx, x, cache, group, inner, write_cache)
         ops.linear(inner, self.w_o, out)
+
+
+_DECAYED_NAMES = dict(q="q", k="k", v="v", gate="g", out="o", norm="norm")
+
+
+@register("mixer", "decayed_linear_attention")
+class DecayedLinearAttention(Mixer):
+    """Linear attention with ONE constant decay per head:
+
+        q = silu(W_q h),  k = silu(W_k h),  v = silu(W_v h)
+        S_t = decay_h S_(t-1) + k_t v_t^T,  o_t = S_t^T q_t           (no other scale)
+
+    The joined heads are RMS-normed together (one weight of heads x dv), multiplied by sigmoid(W_g h) and projected by
+    W_o.  The state is float32 in the request's state slot; the scan is the one of gated linear attention with the
+    head's constant in the place of the decays per channel."""
+
+    takes_lazy_input = True       # x goes to one product only
+    writes_through_linear = True  # out is the out of the last product
+
+    def __init__(self, hidden_size: int, num_heads: int, key_dim: int, value_dim: int, head_decays, norm_eps: float,
+                 names: Optional[dict] = None):
+        if len(head_decays) != num_heads:
+            raise ValueError("one decay per head")
+        self.hidden_size, self.num_heads, self.key_dim, self.value_dim = hidden_size, num_heads, key_dim, value_dim
+        self.head_decays = tuple(float(d) for d in head_decays)
+        self.norm_eps = float(norm_eps)
+        self.names = dict(_DECAYED_NAMES, **(names or {}))
+        self.k_width, self.v_width = num_heads * key_dim, num_heads * value_dim
+        self.inner_width = self.v_width
+        self.input_width = 2 * self.k_width + 2 * self.v_width
+        self.w_in = self.w_o = self.norm_w = self.decays = None
+
+    def cache_spec(self):
+        return FixedStateSpec((self.num_heads, self.value_dim, self.key_dim), torch.float32)
+
+    def weight_specs(self, prefix: str) -> list[WeightSpec]:
+        n, W = self.names, self.hidden_size
+        return [WeightSpec(prefix + n["q"], (self.k_width, W), MATRIX),
+                WeightSpec(prefix + n["k"], (self.k_width, W), MATRIX),
+                WeightSpec(prefix + n["v"], (self.v_width, W), MATRIX),
+                WeightSpec(prefix + n["gate"], (self.v_width, W), MATRIX),
+                WeightSpec(prefix + n["out"], (W, self.v_width), MATRIX),
+                WeightSpec(prefix + n["norm"], (self.v_width,), NORM)]
+
+    def load(self, prefix, source, dtype, device) -> None:
+        n = self.names
+        stacked = torch.cat([source.get(prefix + n[x]) for x in ("q", "k", "v", "gate")], dim=0)
+        self.w_in = ops.prepare_matrix(stacked.to(dtype).to(device))
+        self.w_o = ops.prepare_matrix(source.get(prefix + n["out"]).to(dtype).to(device))
+        self.norm_w = source.get(prefix + n["norm"]).to(torch.float32).to(device).contiguous()
+        self.decays = torch.tensor(self.head_decays, dtype=torch.float32).to(device)
+
+    def first_weights(self):
+        return self.w_in
+
+    def output_weight(self):
+        return self.w_o
+
+    def mix_into(self, ctx: StepContext, x, cache, group, inner, write_cache: bool = True, scale: float = 1.0) -> None:
+        T, H, dk, dv = ctx.num_tokens, self.num_heads, self.key_dim, self.value_dim
+        kw, vw = self.k_width, self.v_width
+        proj = ctx.arena.alloc((T, self.input_width), ctx.dtype)
+        ops.linear(x, self.w_in, proj)
+        # silu of q, k and v in one pass: x sigmoid(x), rounded once
+        qkv = ctx.arena.alloc((T, 2 * kw + vw), ctx.dtype)
+        ops.head_norm_gate(proj[:, :2 * kw + vw], proj[:, :2 * kw + vw], None, 0.0, qkv, 1, 2 * kw + vw, gate_kind="sigmoid")
+        o = ctx.arena.alloc((T, vw), torch.float32)
+        ops.linear_attention_scan(qkv[:, :kw], qkv[:, kw:2 * kw], qkv[:, 2 * kw:], None, cache, ctx, o, 1.0, H, dk, dv,
+                                  write_state=write_cache, head_decay=self.decays)
+        ops.head_norm_gate(o, proj[:, 2 * kw + vw:], self.norm_w, self.norm_eps, inner, 1, vw, gate_kind="sigmoid", scale=scale)
+
+    def forward(self, ctx: StepContext, x, cache, group, out, write_cache: bool = True) -> None:
+        inner = ctx.arena.alloc((ctx.num_tokens, self.inner_width), ctx.dtype)
+        self.mix_into(ctx, x, cache, group, inner, write_cache)
+        ops.linear(inner, self.w_o, out)

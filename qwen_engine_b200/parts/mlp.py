@@ -5,7 +5,8 @@ over the stacked weights.
 
 The same part serves other gated feed-forwards: ``activation`` names the
 function on the gate ("silu", or "gelu_tanh": 0.5 z (1 + tanh(sqrt(2/pi) (z +
-0.044715 z^3)))), ``names`` the three tensors.  The gate/up products that form
+0.044715 z^3)))), or the limited form ("swish_limit", L): g' = min(g, L), u' =
+clamp(u, -L, L), g' sigmoid(1.702 g') (u' + 1); ``names`` the three tensors.  The gate/up products that form
 the activation in their own epilogue take either; the down product that forms
 SiLU-mul while it loads (some tens of rows) is SiLU's alone, so another
 activation runs there as product, activation kernel, product."""
@@ -24,11 +25,11 @@ class SwiGLU(FeedForward):
     writes_through_linear = True  # out is the out of the last product
     def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu",
                  names: tuple = ("gate_proj.weight", "up_proj.weight", "down_proj.weight")):
-        if activation not in ops.GATE_ACTIVATIONS:
-            raise ValueError(f"unknown activation {activation!r}; known: {sorted(ops.GATE_ACTIVATIONS)}")
+        if not ops.gate_activation_known(activation):
+            raise ValueError(f"unknown activation {activation!r}; known: {sorted(ops.GATE_ACTIVATIONS)} and ({ops.LIMITED_GLU!r}, limit)")
         self.hidden_size = hidden_size
         self.intermediate_size = intermediate_size
-        self.activation = activation
+        self.activation = tuple(activation) if isinstance(activation, (tuple, list)) else activation
         self.names = tuple(names)
         self.w_gate_up = self.w_down = None
 

@@ -1,0 +1,67 @@
+"""Routed experts: a mixture of small gated feed-forwards of which every token uses a few.
+
+    z = W_router h + b                      float32, one logit per expert
+    the `top` experts with the largest logits are chosen; their weights are the softmax over the chosen logits alone
+    out = sum over the chosen e of weight_e * W_down,e glu(W_gate,e h, W_up,e h)
+
+The experts' weights are stacked ([E, 2 ff, W] gate rows then up rows, and [E, W, ff]); the (token, choice) pairs
+are ordered by expert on the device and run as tiles of two grouped products, the activation in the first one's
+epilogue.  Nothing of the launches depends on the routing, so steps are replayed from CUDA graphs like any other.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..weights.spec import MATRIX, VECTOR, WeightSpec
+from .base import FeedForward, StepContext, register
+
+
+@register("feed_forward", "routed_experts")
+class RoutedExperts(FeedForward):
+    def __init__(self, hidden_size: int, intermediate_size: int, num_experts: int, top: int, activation="silu",
+                 names: tuple = ("gate", "up", "down"), router_name: str = "router", router_bias_name: str = "router.b",
+                 expert_prefix: str = "e"):
+        if not ops.gate_activation_known(activation):
+            raise ValueError(f"unknown activation {activation!r}")
+        if not (1 <= top <= num_experts):
+            raise ValueError(f"top = {top} of {num_experts} experts")
+        self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+        self.num_experts, self.top = num_experts, top
+        self.activation = tuple(activation) if isinstance(activation, (tuple, list)) else activation
+        self.names, self.router_name, self.router_bias_name, self.expert_prefix = tuple(names), router_name, router_bias_name, expert_prefix
+        self.w_router = self.router_bias = self.w_gate_up = self.w_down = None
+
+    def weight_specs(self, prefix: str) -> list[WeightSpec]:
+        I, W = self.intermediate_size, self.hidden_size
+        gate, up, down = self.names
+        specs = []
+        for e in range(self.num_experts):
+            p = f"{prefix}{self.expert_prefix}{e}."
+            specs += [WeightSpec(p + gate, (I, W), MATRIX), WeightSpec(p + up, (I, W), MATRIX), WeightSpec(p + down, (W, I), MATRIX)]
+        specs += [WeightSpec(prefix + self.router_name, (self.num_experts, W), MATRIX),
+                  WeightSpec(prefix + self.router_bias_name, (self.num_experts,), VECTOR)]
+        return specs
+
+    def load(self, prefix, source, dtype, device) -> None:
+        gate, up, down = self.names
+        gu, dn = [], []
+        for e in range(self.num_experts):
+            p = f"{prefix}{self.expert_prefix}{e}."
+            gu.append(torch.cat([source.get(p + gate), source.get(p + up)], dim=0))
+            dn.append(source.get(p + down))
+        self.w_gate_up = torch.stack(gu).to(dtype).to(device).contiguous()
+        self.w_down = torch.stack(dn).to(dtype).to(device).contiguous()
+        # the router works in float32 whatever the compute type
+        self.w_router = source.get(prefix + self.router_name).to(torch.float32).to(device).contiguous()
+        self.router_bias = source.get(prefix + self.router_bias_name).to(torch.float32).to(device).contiguous()
+
+    def first_weights(self):
+        return None
+
+    def forward(self, ctx: StepContext, x, out) -> None:
+        T = ctx.num_tokens
+        top_idx = ctx.arena.alloc((T, self.top), torch.int32)
+        top_w = ctx.arena.alloc((T, self.top), torch.float32)
+        ops.moe_route(x, self.w_router, self.router_bias, top_idx, top_w)
+        ops.moe_experts(x, top_idx, top_w, self.w_gate_up, self.w_down, out, self.activation, ctx.arena.alloc)

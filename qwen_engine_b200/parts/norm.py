@@ -8,6 +8,8 @@ here the stream is float32 and the add happens inside the norm kernel.
 
 ``weight_offset``: a design may store the scale around zero and multiply by
 (offset + w); the sum is formed once, in float32, when the weights are loaded.
+``output_scale``: a constant that multiplies the normed rows (a model's scale of
+its logits, on the final norm), folded into the weight in float32 at load.
 """
 from __future__ import annotations
 
@@ -22,11 +24,13 @@ from .base import Norm, StepContext, register
 
 @register("norm", "rmsnorm")
 class RMSNorm(Norm):
-    def __init__(self, width: int, eps: float, weight_name: str = "weight", weight_offset: float = 0.0):
+    def __init__(self, width: int, eps: float, weight_name: str = "weight", weight_offset: float = 0.0,
+                 output_scale: float = 1.0):
         self.width = width
         self.eps = float(eps)
         self.weight_name = weight_name
         self.weight_offset = float(weight_offset)
+        self.output_scale = float(output_scale)
         self.weight: Optional[torch.Tensor] = None
 
     def weight_specs(self, prefix: str) -> list[WeightSpec]:
@@ -37,6 +41,8 @@ class RMSNorm(Norm):
         w = source.get(prefix + self.weight_name).to(torch.float32)
         if self.weight_offset:
             w = w + self.weight_offset
+        if self.output_scale != 1.0:
+            w = w * self.output_scale
         self.weight = w.to(device).contiguous()
 
     def normed(self, ctx: StepContext, stream, lazy: bool = False):

@@ -11,8 +11,9 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Any, Callable
 
-from .config import ConfigError, GanidraConfig, ModelConfig, Qwen3Config, read_config_json
+from .config import BesavikConfig, ConfigError, GanidraConfig, ModelConfig, Qwen3Config, read_config_json
 from .models.decoder import DecoderModel, ModelLayout
+from .models.besavik import besavik_layout
 from .models.ganidra import ganidra_layout
 from .models.qwen3 import qwen3_layout
 
@@ -33,6 +34,7 @@ def register_architecture(name: str, config_class: type, layout: Callable[[Any],
 
 register_architecture("Qwen3ForCausalLM", Qwen3Config, qwen3_layout)
 register_architecture("Ganidra", GanidraConfig, ganidra_layout)
+register_architecture("Besavik", BesavikConfig, besavik_layout)
 
 
 def architecture_of(raw_config: dict[str, Any]) -> Architecture:

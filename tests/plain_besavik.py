@@ -1,0 +1,166 @@
+"""Besavik, written down plainly: one function per mechanism, float64, token by
+token where the design is a recurrence, no cache, no batch, no code of the
+package.  The tests compare the engine with this.
+
+Notation: h is a mixer's input [T, W] (the normed stream), weights are a dict
+name -> tensor stored [out, in] and applied as W h.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+F64 = torch.float64
+
+
+def rms_norm(x, w, eps):
+    return x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * w
+
+
+def rotate_half_pairs(x, positions, base, dims):
+    """x [T, ..., D]: the first ``dims`` channels are rotated, channel i with channel i + dims/2, by the
+    angle position * base^(-2i/dims); the rest pass."""
+    half = dims // 2
+    i = torch.arange(half, dtype=F64)
+    freq = base ** (-2.0 * i / dims)
+    ang = positions.to(F64)[:, None] * freq[None, :]                 # [T, half]
+    shape = [x.shape[0]] + [1] * (x.dim() - 2) + [half]
+    cos, sin = torch.cos(ang).reshape(shape), torch.sin(ang).reshape(shape)
+    u, v = x[..., :half], x[..., half:dims]
+    out = x.clone()
+    out[..., :half] = u * cos - v * sin
+    out[..., half:dims] = v * cos + u * sin
+    return out
+
+
+def latent_attention(h, w, p, m, eps, positions=None):
+    """Softmax attention whose keys and values are read out of a small latent per token, with one rotated key
+    part shared by all heads.  m: heads, dim, rot_dim, vdim, kv_rank, q_rank, scale, rot {base, dims}."""
+    T = h.shape[0]
+    H, dn, dr, dv, r = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+    pos = torch.arange(T) if positions is None else positions
+    cq = rms_norm(h @ w[p + "dq"].T, w[p + "dq.norm"], eps)
+    q = (cq @ w[p + "uq"].T).reshape(T, H, dn + dr)
+    q_plain, q_rot = q[..., :dn], q[..., dn:]
+    down = h @ w[p + "dkv"].T
+    c = rms_norm(down[:, :r], w[p + "dkv.norm"], eps)
+    k_rot = down[:, r:]                                               # [T, dr], one for all heads
+    base, dims = m["rot"]["base"], m["rot"]["dims"]
+    q_rot = rotate_half_pairs(q_rot, pos, base, dims)
+    k_rot = rotate_half_pairs(k_rot, pos, base, dims)
+    k_plain = (c @ w[p + "uk"].T).reshape(T, H, dn)
+    v = (c @ w[p + "uv"].T).reshape(T, H, dv)
+    out = torch.zeros(T, H, dv, dtype=F64)
+    for i in range(T):
+        s = (torch.einsum("hd,jhd->hj", q_plain[i], k_plain[:i + 1])
+             + torch.einsum("hd,jd->hj", q_rot[i], k_rot[:i + 1])) * m["scale"]
+        a = torch.softmax(s, dim=-1)
+        out[i] = torch.einsum("hj,jhd->hd", a, v[:i + 1])
+    gate = torch.sigmoid(h @ w[p + "g"].T)
+    return (out.reshape(T, H * dv) * gate) @ w[p + "o"].T
+
+
+def lightning(h, w, p, m, eps):
+    """Linear attention with one constant decay per head: S <- decay S + k v^T, o = S^T q."""
+    T = h.shape[0]
+    H, dk, dv = m["heads"], m["dim"], m["vdim"]
+    silu = torch.nn.functional.silu
+    q = silu(h @ w[p + "q"].T).reshape(T, H, dk)
+    k = silu(h @ w[p + "k"].T).reshape(T, H, dk)
+    v = silu(h @ w[p + "v"].T).reshape(T, H, dv)
+    decay = torch.tensor(m["decay"], dtype=F64)
+    S = torch.zeros(H, dk, dv, dtype=F64)
+    o = torch.zeros(T, H, dv, dtype=F64)
+    for t in range(T):
+        S = decay[:, None, None] * S + k[t][:, :, None] * v[t][:, None, :]
+        o[t] = torch.einsum("hkv,hk->hv", S, q[t])
+    y = rms_norm(o.reshape(T, H * dv), w[p + "norm"], eps) * torch.sigmoid(h @ w[p + "g"].T)
+    return y @ w[p + "o"].T
+
+
+def short_conv(x, taps_w):
+    """x [T, C]; taps_w [C, taps], the last column is the current token's; zeros before the start."""
+    T, C = x.shape
+    taps = taps_w.shape[1]
+    padded = torch.cat([torch.zeros(taps - 1, C, dtype=x.dtype), x], dim=0)
+    y = torch.zeros_like(x)
+    for j in range(taps):
+        y = y + padded[j:j + T] * taps_w[:, j][None, :]
+    return y
+
+
+def channel_delta(h, w, p, m, eps):
+    """The gated delta rule with one decay per head and key channel."""
+    T = h.shape[0]
+    H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    silu = torch.nn.functional.silu
+    q = silu(short_conv(h @ w[p + "q"].T, w[p + "q.conv"])).reshape(T, G, dk)
+    k = silu(short_conv(h @ w[p + "k"].T, w[p + "k.conv"])).reshape(T, G, dk)
+    v = silu(short_conv(h @ w[p + "v"].T, w[p + "v.conv"])).reshape(T, H, dv)
+    q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + 1e-6) * dk ** -0.5
+    k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
+    beta = torch.sigmoid(h @ w[p + "b"].T)                           # [T, H]
+    z = (h @ w[p + "a1"].T) @ w[p + "a2"].T + w[p + "dt_bias"]
+    rate = torch.exp(w[p + "A_log"])                                 # [H]
+    g = torch.exp(-rate[None, :, None] * torch.nn.functional.softplus(z).reshape(T, H, dk))
+    S = torch.zeros(H, dk, dv, dtype=F64)
+    o = torch.zeros(T, H, dv, dtype=F64)
+    rep = H // G
+    for t in range(T):
+        qt = q[t].repeat_interleave(rep, dim=0)                       # head h reads q/k head h // rep
+        kt = k[t].repeat_interleave(rep, dim=0)
+        S = g[t][:, :, None] * S
+        u = beta[t][:, None] * (v[t] - torch.einsum("hkv,hk->hv", S, kt))
+        S = S + kt[:, :, None] * u[:, None, :]
+        o[t] = torch.einsum("hkv,hk->hv", S, qt)
+    o = o / torch.sqrt((o * o).mean(-1, keepdim=True) + eps) * w[p + "norm"]
+    gate = torch.sigmoid((h @ w[p + "g1"].T) @ w[p + "g2"].T)
+    return (o.reshape(T, H * dv) * gate) @ w[p + "o"].T
+
+
+def limited_glu(h, w_gate, w_up, w_down, limit):
+    g = torch.clamp(h @ w_gate.T, max=limit)
+    u = torch.clamp(h @ w_up.T, -limit, limit)
+    return (g * torch.sigmoid(1.702 * g) * (u + 1.0)) @ w_down.T
+
+
+def dense_ff(h, w, p, mlp):
+    return limited_glu(h, w[p + "gate"], w[p + "up"], w[p + "down"], mlp["limit"])
+
+
+def moe_ff(h, w, p, mlp):
+    E, top = mlp["router"]["experts"], mlp["router"]["top"]
+    z = h @ w[p + "router"].T + w[p + "router.b"]
+    val, idx = torch.topk(z, top, dim=-1)
+    wgt = torch.softmax(val, dim=-1)
+    out = torch.zeros_like(h)
+    for t in range(h.shape[0]):
+        for j in range(top):
+            e = int(idx[t, j])
+            pe = f"{p}e{e}."
+            out[t] += wgt[t, j] * limited_glu(h[t:t + 1], w[pe + "gate"], w[pe + "up"], w[pe + "down"],
+                                              mlp["expert"]["limit"])[0]
+    return out
+
+
+MIXERS = {"latent_attention": latent_attention, "lightning": lightning, "channel_delta": channel_delta}
+
+
+def forward(cfg: dict, weights: dict, tokens, return_layers: bool = False):
+    """Logits [T, vocab] of one sequence (and the stream after every layer)."""
+    w = {k: v.to(F64) for k, v in weights.items()}
+    eps = cfg["norm"]["eps"]
+    x = rms_norm(w["embed"][torch.as_tensor(tokens, dtype=torch.long)], w["embed.norm"], eps)
+    after = []
+    for i, layer in enumerate(cfg["layers"]):
+        p = f"l{i}."
+        h = rms_norm(x, w[p + "norm1"], eps)
+        x = x + MIXERS[layer["type"]](h, w, p + "mix.", layer["mixer"], eps)
+        mlp = layer.get("mlp")
+        if mlp is not None:
+            h = rms_norm(x, w[p + "norm2"], eps)
+            x = x + (dense_ff if mlp["kind"] == "dense" else moe_ff)(h, w, p + "mlp.", mlp)
+        after.append(x.clone())
+    logits = rms_norm(x, w["final.norm"], eps) @ w["embed"].T * cfg["logit_scale"]
+    return (logits, torch.stack(after)) if return_layers else logits

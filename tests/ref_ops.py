@@ -152,7 +152,8 @@ def paged_attention(qkv, kv_pages, block_tables, ctx, out, scale, window, num_he
         assert bool((pages[needed] >= 0).all()), "attention needs a key whose page was given back"
         pages = pages.clamp(min=0)
         k = kv_pages[pages, 0, :, kpos % P, :].to(torch.float32)      # [total, Hkv, D]
-        v = kv_pages[pages, 1, :, kpos % P, :].to(torch.float32)
+        # (a cache of one plane: the values are the keys' channels)
+        v = kv_pages[pages, kv_pages.shape[1] - 1, :, kpos % P, :].to(torch.float32)
         k = torch.where(needed[:, None, None], k, torch.zeros_like(k))
         v = torch.where(needed[:, None, None], v, torch.zeros_like(v))
         for h in range(Hq):
@@ -180,22 +181,34 @@ def act_mul(gate_up, out, activation="silu"):
         a = g / (1.0 + torch.exp(-g))
     elif activation == "gelu_tanh":
         a = 0.5 * g * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (g + 0.044715 * g ** 3)))
+    elif isinstance(activation, (tuple, list)) and activation[0] == "swish_limit":
+        lim = float(activation[1])
+        g = torch.clamp(g, max=lim)
+        u = torch.clamp(u, -lim, lim) + 1.0
+        a = g * torch.sigmoid(1.702 * g)
     else:
         raise ValueError(activation)
     out.copy_((a * u).to(out.dtype))
 
 
-def channel_decay(a, w, bias, tau, out):
+def channel_decay(a, w, bias, tau, out, log_rate=None):
     z = a.to(torch.float32) @ w.to(torch.float32).t()
     if bias is not None:
         z = z + bias
-    out.copy_(torch.exp(torch.nn.functional.logsigmoid(z) / tau))
+    if log_rate is not None:
+        rate = torch.exp(log_rate).repeat_interleave(z.shape[1] // log_rate.numel())
+        out.copy_(torch.exp(-rate * torch.nn.functional.softplus(z)))
+    else:
+        out.copy_(torch.exp(torch.nn.functional.logsigmoid(z) / tau))
 
 
-def linear_attention_scan(q, k, v, alpha, state, ctx, out, q_scale, num_heads, key_dim, value_dim, write_state=True, decay=None):
+def linear_attention_scan(q, k, v, alpha, state, ctx, out, q_scale, num_heads, key_dim, value_dim, write_state=True, decay=None,
+                          head_decay=None):
     """state [slots, H, dv, dk]; per request and head, token by token."""
     H, dk, dv = num_heads, key_dim, value_dim
-    if alpha is None:
+    if head_decay is not None:
+        alpha = head_decay.to(torch.float32).repeat_interleave(dk)[None, :].expand(q.shape[0], H * dk)
+    elif alpha is None:
         a, w, bias, tau = decay
         alpha = torch.empty(q.shape[0], H * dk, dtype=torch.float32)
         channel_decay(a, w, bias, tau, alpha)
@@ -225,6 +238,107 @@ def head_norm_gate(x, gate, weight, eps, out, num_heads, head_dim, gate_kind="si
         g = gate.to(torch.float32).reshape(T, num_heads, head_dim)
         y = y * (g / (1.0 + torch.exp(-g)) if gate_kind == "silu" else torch.sigmoid(g))
     out.copy_((y * scale).reshape(T, num_heads * head_dim).to(out.dtype))
+
+
+def latent_prepare(down, q, norm_w, eps, positions, inv_freq, rot_dims, cache, slot_mapping, qlat, num_heads, plain_dim,
+                   latent_dim, rot_dim, write_kv=True):
+    T, H, dn, R, Dr = q.shape[0], num_heads, plain_dim, latent_dim, rot_dim
+    D, P = R + Dr, cache.shape[3]
+    half = rot_dims // 2
+    ang = positions.to(torch.float32)[:, None] * inv_freq[:half][None, :]
+    cos, sin = torch.cos(ang), torch.sin(ang)
+
+    def turn(x):                       # [T, ..., Dr]
+        x = x.to(torch.float32).clone()
+        shape = [T] + [1] * (x.dim() - 2) + [half]
+        u, v = x[..., :half].clone(), x[..., half:rot_dims].clone()
+        x[..., :half] = u * cos.reshape(shape) - v * sin.reshape(shape)
+        x[..., half:rot_dims] = v * cos.reshape(shape) + u * sin.reshape(shape)
+        return x
+    if write_kv:
+        row = torch.cat([_rms(down[:, :R], norm_w, eps), turn(down[:, R:])], dim=1).to(cache.dtype)
+        slots = slot_mapping.long()
+        cache[slots // P, 0, 0, slots % P] = row
+    out = qlat.view(T, H, D)
+    out[:, :, R:] = turn(q.reshape(T, H, dn + Dr)[:, :, dn:]).to(qlat.dtype)
+
+
+def head_linear(x, w, out, x_head_stride, out_head_stride):
+    H, N, K = w.shape
+    for h in range(H):
+        xs = x[:, h * x_head_stride:h * x_head_stride + K].to(torch.float32)
+        out[:, h * out_head_stride:h * out_head_stride + N] = (xs @ w[h].to(torch.float32).t()).to(out.dtype)
+
+
+def short_conv(x, w, state, ctx, out, write_state=True, silu=True):
+    taps = w.shape[1]
+    hist = taps - 1
+    cu, ctx_lens, slots = ctx.cu_q.tolist(), ctx.ctx_lens.tolist(), ctx.slot_ids.tolist()
+    for r in range(len(ctx_lens)):
+        a, b = cu[r], cu[r + 1]
+        if b <= a:
+            continue
+        old = state[slots[r]].clone() if ctx_lens[r] > 0 else torch.zeros_like(state[slots[r]])     # [hist, C]
+        seq = torch.cat([old, x[a:b].to(torch.float32)], dim=0)
+        y = torch.zeros(b - a, x.shape[1], dtype=torch.float32)
+        for j in range(taps):
+            y = y + seq[j:j + b - a] * w[:, j][None, :]
+        out[a:b] = y * torch.sigmoid(y) if silu else y
+        if write_state and hist > 0:
+            state[slots[r]] = seq[-hist:]
+
+
+def unit_norm(x, num_heads, head_dim, eps, scale=1.0):
+    T = x.shape[0]
+    y = x.reshape(T, num_heads, head_dim)
+    y = y * torch.rsqrt((y * y).sum(dim=-1, keepdim=True) + eps) * scale
+    x.copy_(y.reshape(T, num_heads * head_dim))
+
+
+def delta_rule_scan(q, k, v, g, beta, state, ctx, out, num_heads, num_key_heads, key_dim, value_dim, write_state=True):
+    H, G, dk, dv = num_heads, num_key_heads, key_dim, value_dim
+    rep = H // G
+    cu, ctx_lens, slots = ctx.cu_q.tolist(), ctx.ctx_lens.tolist(), ctx.slot_ids.tolist()
+    for r in range(len(ctx_lens)):
+        a, b = cu[r], cu[r + 1]
+        if b <= a:
+            continue
+        S = state[slots[r]].clone() if ctx_lens[r] > 0 else torch.zeros_like(state[slots[r]])     # [H, dv, dk]
+        for t in range(a, b):
+            qt = q[t].reshape(G, dk).repeat_interleave(rep, dim=0)
+            kt = k[t].reshape(G, dk).repeat_interleave(rep, dim=0)
+            vt = v[t].reshape(H, dv)
+            if g is not None:
+                S = S * g[t].reshape(H, dk)[:, None, :]
+            bt = torch.sigmoid(beta[t].to(torch.float32))
+            u = bt[:, None] * (vt - (S * kt[:, None, :]).sum(dim=-1))
+            S = S + u[:, :, None] * kt[:, None, :]
+            out[t] = (S * qt[:, None, :]).sum(dim=-1).reshape(H * dv)
+        if write_state:
+            state[slots[r]] = S
+
+
+def moe_route(x, w, bias, top_idx, top_w):
+    z = x.to(torch.float32) @ w.t()
+    if bias is not None:
+        z = z + bias
+    val, idx = torch.topk(z, top_idx.shape[1], dim=-1)
+    top_idx.copy_(idx.to(torch.int32))
+    top_w.copy_(torch.softmax(val, dim=-1))
+
+
+def moe_experts(x, top_idx, top_w, w_gate_up, w_down, out, activation, alloc):
+    T = x.shape[0]
+    I = w_gate_up.shape[1] // 2
+    acc = torch.zeros(T, w_down.shape[1], dtype=torch.float32)
+    for t in range(T):
+        for j in range(top_idx.shape[1]):
+            e = int(top_idx[t, j])
+            gu = (x[t:t + 1].to(torch.float32) @ w_gate_up[e].to(torch.float32).t()).to(x.dtype)
+            act = torch.empty(1, I, dtype=x.dtype)
+            act_mul(gu, act, activation)
+            acc[t] += float(top_w[t, j]) * (act.to(torch.float32) @ w_down[e].to(torch.float32).t())[0]
+    out.copy_(acc.to(out.dtype))
 
 
 def scaled_add(acc, x, scale, first=False):
@@ -286,7 +400,8 @@ def copy_pages(cache, pairs):
         cache[:, dst] = cache[:, src].clone()
 
 
-_NAMES = ["act_mul", "channel_decay", "linear_attention_scan", "head_norm_gate", "scaled_add", "copy_pages", "swiglu_small_applies", "qkv_rope_small_applies", "prepare_matrix", "embedding", "add_rmsnorm", "add_rmsnorm_rows", "linear",
+_NAMES = ["latent_prepare", "head_linear", "short_conv", "unit_norm", "delta_rule_scan", "moe_route", "moe_experts",
+          "act_mul", "channel_decay", "linear_attention_scan", "head_norm_gate", "scaled_add", "copy_pages", "swiglu_small_applies", "qkv_rope_small_applies", "prepare_matrix", "embedding", "add_rmsnorm", "add_rmsnorm_rows", "linear",
           "qk_norm_rope_kv_write", "rope_neox", "rope_table", "place_tokens", "swiglu_fused_applies", "plan_attention", "paged_attention", "silu_mul", "linear_silu_mul",
           "argmax", "sample"]
 
