@@ -1,5 +1,5 @@
 // Attention of a step's new queries over the paged cache, for any mixture of prompt portions
-// and single decoded tokens, any head size up to 512, any page size, any number of heads and
+// and single decoded tokens, any head size up to 640, any page size, any number of heads and
 // groups, float32 or bfloat16 storage; all arithmetic in float32 with expf.
 //
 // For the query at position i of a request, key j is allowed iff j <= i and (window == 0 or
@@ -18,9 +18,9 @@
 #define AG_BM 16
 #define AG_BN 32
 #define AG_WARPS 4
-#define AG_MAX_D 512
+#define AG_MAX_D 640       // (heads beyond 512 channels run an instantiation with more accumulators a lane)
 
-template <typename T>
+template <typename T, int DREG>
 __global__ void __launch_bounds__(AG_WARPS * 32)
 attention_generic_kernel(const T* __restrict__ q, long q_stride, const T* __restrict__ pages,
                          const int* __restrict__ block_tables, int max_blocks,
@@ -51,7 +51,6 @@ attention_generic_kernel(const T* __restrict__ q, long q_stride, const T* __rest
   }
 
   constexpr int QPW = AG_BM / AG_WARPS;       // queries per warp
-  constexpr int DREG = AG_MAX_D / 32;
   float m[QPW], l[QPW];
   float acc[QPW][DREG];
 #pragma unroll
@@ -142,20 +141,21 @@ extern "C" int qe_paged_attention_generic(const void* q, long q_stride, const vo
   static bool configured = false;
   if (!configured) {
     const int max_smem = (int)(((size_t)AG_BM * AG_MAX_D + (size_t)AG_BN * (AG_MAX_D + 1) + (size_t)AG_BN * AG_MAX_D) * sizeof(float));
-    cudaError_t e = cudaFuncSetAttribute(attention_generic_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_generic_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    cudaError_t e = cudaFuncSetAttribute(attention_generic_kernel<float, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_generic_kernel<__nv_bfloat16, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_generic_kernel<float, AG_MAX_D / 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_generic_kernel<__nv_bfloat16, AG_MAX_D / 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
     if (e != cudaSuccess) QE_REFUSE("paged_attention: shared memory %d: %s", max_smem, cudaGetErrorString(e));
     configured = true;
   }
-  if (dtype == QE_DTYPE_F32) {
-    qe_launch(attention_generic_kernel<float>, grid, dim3(AG_WARPS * 32), smem, stream,
-        (const float*)q, q_stride, (const float*)pages, block_tables, max_blocks, cu_q, ctx_lens, tiles,
-        (float*)out, scale, window, Hq, Hkv, D, page_size, slopes, kv_planes == 1 ? 1 : 2);
-  } else if (dtype == QE_DTYPE_BF16) {
-    qe_launch(attention_generic_kernel<__nv_bfloat16>, grid, dim3(AG_WARPS * 32), smem, stream,
-        (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)pages, block_tables, max_blocks, cu_q, ctx_lens,
-        tiles, (__nv_bfloat16*)out, scale, window, Hq, Hkv, D, page_size, slopes, kv_planes == 1 ? 1 : 2);
-  } else QE_REFUSE("paged_attention: unknown dtype %d", dtype);
+  const int planes = kv_planes == 1 ? 1 : 2;
+#define AGL(TT, DR) qe_launch(attention_generic_kernel<TT, DR>, grid, dim3(AG_WARPS * 32), smem, stream, (const TT*)q, q_stride, \
+                              (const TT*)pages, block_tables, max_blocks, cu_q, ctx_lens, tiles, (TT*)out, scale, window, Hq, Hkv, D, \
+                              page_size, slopes, planes)
+  if (dtype == QE_DTYPE_F32) { if (D <= 512) AGL(float, 16); else AGL(float, AG_MAX_D / 32); }
+  else if (dtype == QE_DTYPE_BF16) { if (D <= 512) AGL(__nv_bfloat16, 16); else AGL(__nv_bfloat16, AG_MAX_D / 32); }
+  else QE_REFUSE("paged_attention: unknown dtype %d", dtype);
+#undef AGL
   QE_CHECK_LAUNCH("paged_attention_generic");
   return 0;
 }

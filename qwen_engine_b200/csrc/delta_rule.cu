@@ -18,7 +18,7 @@
 // channel; inputs before the step's first token come from the request's state (its last taps - 1 inputs; zeros for a
 // request without context), and the state is moved on.  x in the compute type, rows strided; y, w, state float32.
 // ---------------------------------------------------------------------------------------------------------
-#define SC_MAX_TAPS 8
+#define SC_MAX_TAPS 16
 #define SC_TOKENS 32
 
 template <typename T>
@@ -134,7 +134,7 @@ extern "C" int qe_unit_norm(float* x, long ld, int T, int H, int D, float eps, f
 // ---------------------------------------------------------------------------------------------------------
 // the scan
 // ---------------------------------------------------------------------------------------------------------
-#define DR_CHUNK 16
+#define DR_MAX_CHUNK 16        // tokens staged at a time (fewer where a head's rows are long)
 #define DR_MAX_THREADS 128
 
 struct DeltaArgs {
@@ -143,7 +143,7 @@ struct DeltaArgs {
   const void* beta; long ld_beta; int beta_dtype;                   // [T, H] before the sigmoid, compute type; null: beta = 1
   const float* head_decay;                                          // with g null: one decay per head, or null for none
   float* state; const int* cu_q; const int* ctx_lens; const int* slot_ids; float* out;
-  int H, G, dk, dv, L, VT, write_state, delta;
+  int H, G, dk, dv, L, VT, write_state, delta, chunk;
 };
 
 __device__ __forceinline__ void dr_cp_async4(float* dst, const float* src) {
@@ -165,7 +165,7 @@ delta_rule_scan_kernel(DeltaArgs A) {
   const int padded = L * DC;
   const int row_w = dr_pad<DC>(padded);                 // floats of a staged row of q, k or g
   const int tok_w = 3 * row_w + ((VT + 3) & ~3) + 4;    // + v of the tile + beta (and padding to 16 bytes)
-  float* buf[2] = {smem, smem + (size_t)DR_CHUNK * tok_w};
+  float* buf[2] = {smem, smem + (size_t)A.chunk * tok_w};
   const int tid = threadIdx.x;
   const int j = j0 + tid / L, l = tid % L;
   const bool owns = tid < VT * L && j < dv;
@@ -190,10 +190,10 @@ delta_rule_scan_kernel(DeltaArgs A) {
   const bool vec = (dk % 4 == 0) && (dv % 4 == 0) && (VT % 4 == 0) &&
                    ((((uintptr_t)A.q | (uintptr_t)A.k | (uintptr_t)A.v | (uintptr_t)A.g) & 15) == 0) &&
                    ((A.ldq | A.ldk | A.ldv | A.ldg) % 4 == 0);
-  const int n_chunks = (n + DR_CHUNK - 1) / DR_CHUNK;
+  const int n_chunks = (n + A.chunk - 1) / A.chunk;
 
   // channels beyond the head and a constant decay are set once, in both buffers; the copies never touch them
-  for (int e = tid; e < 2 * DR_CHUNK * padded; e += blockDim.x) {
+  for (int e = tid; e < 2 * A.chunk * padded; e += blockDim.x) {
     const int t = e / padded, c = e - t * padded;
     float* dst = smem + (size_t)t * tok_w + dr_pad<DC>(c);
     if (c >= dk) { dst[0] = 0.f; dst[row_w] = 0.f; dst[2 * row_w] = 1.f; }
@@ -201,8 +201,8 @@ delta_rule_scan_kernel(DeltaArgs A) {
   }
   auto stage = [&](int ch) {
     float* b = buf[ch & 1];
-    const int t_first = ch * DR_CHUNK;
-    const int rows = min(DR_CHUNK, n - t_first);
+    const int t_first = ch * A.chunk;
+    const int rows = min(A.chunk, n - t_first);
     if (vec) {
       const int pk = dk / 4, pv = VT / 4;
       const int per_tok = (g ? 3 : 2) * pk + pv;
@@ -257,10 +257,10 @@ delta_rule_scan_kernel(DeltaArgs A) {
     else asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     __syncthreads();
     if (owns) {
-      const int rows = min(DR_CHUNK, n - ch * DR_CHUNK);
+      const int rows = min(A.chunk, n - ch * A.chunk);
       const float* r = buf[ch & 1] + l * (DC + 4);
       const float* rv = buf[ch & 1] + 3 * row_w;
-      float* o = A.out + (size_t)(row0 + ch * DR_CHUNK) * o_ld + (size_t)head * dv + j;
+      float* o = A.out + (size_t)(row0 + ch * A.chunk) * o_ld + (size_t)head * dv + j;
       for (int t = 0; t < rows; ++t) {
         float ks0 = 0.f, ks1 = 0.f, qs0 = 0.f, qs1 = 0.f, qk0 = 0.f, qk1 = 0.f;
         float kr[DC];
@@ -322,7 +322,10 @@ extern "C" int qe_delta_rule_scan(const float* q, long ldq, const float* k, long
   A.VT = VT;
   const int row_w = L * DC + ((L * DC) / DC) * 4;
   const int tok_w = 3 * row_w + ((VT + 3) & ~3) + 4;
-  const size_t smem = (size_t)2 * DR_CHUNK * tok_w * sizeof(float);
+  int chunk = DR_MAX_CHUNK;
+  while (chunk > 1 && (size_t)2 * chunk * tok_w * sizeof(float) > 200 * 1024) chunk >>= 1;
+  A.chunk = chunk;
+  const size_t smem = (size_t)2 * A.chunk * tok_w * sizeof(float);
   if (smem > 200 * 1024) QE_REFUSE("delta_rule_scan: key size %d needs %zu bytes of shared memory", dk, smem);
   const int threads = ((VT * L + 31) / 32) * 32;
 #define DRL(DCC) do { \
