@@ -34,6 +34,19 @@ def rotate_half_pairs(x, positions, base, dims):
     return out
 
 
+def latent_softmax(q_plain, q_rot, k_plain, k_rot, v, scale, first=0):
+    """Causal softmax attention with a key part that all heads share.  q_plain [n, H, dn], q_rot [n, H, dr] (already
+    rotated) are the queries at positions first .. first + n - 1; k_plain [t, H, dn], k_rot [t, dr], v [t, H, dv]
+    the keys and values of positions 0 .. t - 1."""
+    n, H = q_plain.shape[:2]
+    out = torch.zeros(n, H, v.shape[-1], dtype=F64)
+    for i in range(n):
+        last = first + i + 1
+        s = (torch.einsum("hd,jhd->hj", q_plain[i], k_plain[:last]) + torch.einsum("hd,jd->hj", q_rot[i], k_rot[:last])) * scale
+        out[i] = torch.einsum("hj,jhd->hd", torch.softmax(s, dim=-1), v[:last])
+    return out
+
+
 def latent_attention(h, w, p, m, eps, positions=None):
     """Softmax attention whose keys and values are read out of a small latent per token, with one rotated key
     part shared by all heads.  m: heads, dim, rot_dim, vdim, kv_rank, q_rank, scale, rot {base, dims}."""
@@ -51,14 +64,20 @@ def latent_attention(h, w, p, m, eps, positions=None):
     k_rot = rotate_half_pairs(k_rot, pos, base, dims)
     k_plain = (c @ w[p + "uk"].T).reshape(T, H, dn)
     v = (c @ w[p + "uv"].T).reshape(T, H, dv)
-    out = torch.zeros(T, H, dv, dtype=F64)
-    for i in range(T):
-        s = (torch.einsum("hd,jhd->hj", q_plain[i], k_plain[:i + 1])
-             + torch.einsum("hd,jd->hj", q_rot[i], k_rot[:i + 1])) * m["scale"]
-        a = torch.softmax(s, dim=-1)
-        out[i] = torch.einsum("hj,jhd->hd", a, v[:i + 1])
+    out = latent_softmax(q_plain, q_rot, k_plain, k_rot, v, m["scale"])
     gate = torch.sigmoid(h @ w[p + "g"].T)
     return (out.reshape(T, H * dv) * gate) @ w[p + "o"].T
+
+
+def decayed_recurrence(q, k, v, decay, S=None):
+    """S <- decay_h S + k v^T, o = S^T q per head; q, k [T, H, dk], v [T, H, dv], decay [H].  Returns o and the last S."""
+    T, H, dk = q.shape
+    S = torch.zeros(H, dk, v.shape[-1], dtype=F64) if S is None else S
+    o = torch.zeros(T, H, v.shape[-1], dtype=F64)
+    for t in range(T):
+        S = decay[:, None, None] * S + k[t][:, :, None] * v[t][:, None, :]
+        o[t] = torch.einsum("hkv,hk->hv", S, q[t])
+    return o, S
 
 
 def lightning(h, w, p, m, eps):
@@ -69,12 +88,7 @@ def lightning(h, w, p, m, eps):
     q = silu(h @ w[p + "q"].T).reshape(T, H, dk)
     k = silu(h @ w[p + "k"].T).reshape(T, H, dk)
     v = silu(h @ w[p + "v"].T).reshape(T, H, dv)
-    decay = torch.tensor(m["decay"], dtype=F64)
-    S = torch.zeros(H, dk, dv, dtype=F64)
-    o = torch.zeros(T, H, dv, dtype=F64)
-    for t in range(T):
-        S = decay[:, None, None] * S + k[t][:, :, None] * v[t][:, None, :]
-        o[t] = torch.einsum("hkv,hk->hv", S, q[t])
+    o, _ = decayed_recurrence(q, k, v, torch.tensor(m["decay"], dtype=F64))
     y = rms_norm(o.reshape(T, H * dv), w[p + "norm"], eps) * torch.sigmoid(h @ w[p + "g"].T)
     return y @ w[p + "o"].T
 
@@ -88,6 +102,20 @@ def short_conv(x, taps_w):
     for j in range(taps):
         y = y + padded[j:j + T] * taps_w[:, j][None, :]
     return y
+
+
+def delta_recurrence(q, k, v, g, beta, S=None):
+    """S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q per head, in this order.  q, k, g [T, H, dk]
+    (q and k already repeated for the heads of a group), v [T, H, dv], beta [T, H].  Returns o and the last S."""
+    T, H, dk = q.shape
+    S = torch.zeros(H, dk, v.shape[-1], dtype=F64) if S is None else S
+    o = torch.zeros(T, H, v.shape[-1], dtype=F64)
+    for t in range(T):
+        S = g[t][:, :, None] * S
+        u = beta[t][:, None] * (v[t] - torch.einsum("hkv,hk->hv", S, k[t]))
+        S = S + k[t][:, :, None] * u[:, None, :]
+        o[t] = torch.einsum("hkv,hk->hv", S, q[t])
+    return o, S
 
 
 def channel_delta(h, w, p, m, eps):
@@ -104,16 +132,8 @@ def channel_delta(h, w, p, m, eps):
     z = (h @ w[p + "a1"].T) @ w[p + "a2"].T + w[p + "dt_bias"]
     rate = torch.exp(w[p + "A_log"])                                 # [H]
     g = torch.exp(-rate[None, :, None] * torch.nn.functional.softplus(z).reshape(T, H, dk))
-    S = torch.zeros(H, dk, dv, dtype=F64)
-    o = torch.zeros(T, H, dv, dtype=F64)
-    rep = H // G
-    for t in range(T):
-        qt = q[t].repeat_interleave(rep, dim=0)                       # head h reads q/k head h // rep
-        kt = k[t].repeat_interleave(rep, dim=0)
-        S = g[t][:, :, None] * S
-        u = beta[t][:, None] * (v[t] - torch.einsum("hkv,hk->hv", S, kt))
-        S = S + kt[:, :, None] * u[:, None, :]
-        o[t] = torch.einsum("hkv,hk->hv", S, qt)
+    rep = H // G                                                      # head h reads q/k head h // rep
+    o, _ = delta_recurrence(q.repeat_interleave(rep, dim=1), k.repeat_interleave(rep, dim=1), v, g, beta)
     o = o / torch.sqrt((o * o).mean(-1, keepdim=True) + eps) * w[p + "norm"]
     gate = torch.sigmoid((h @ w[p + "g1"].T) @ w[p + "g2"].T)
     return (o.reshape(T, H * dv) * gate) @ w[p + "o"].T
@@ -129,11 +149,16 @@ def dense_ff(h, w, p, mlp):
     return limited_glu(h, w[p + "gate"], w[p + "up"], w[p + "down"], mlp["limit"])
 
 
-def moe_ff(h, w, p, mlp):
-    E, top = mlp["router"]["experts"], mlp["router"]["top"]
-    z = h @ w[p + "router"].T + w[p + "router.b"]
+def route(h, w_router, bias, top):
+    """The experts a token uses and their weights: the `top` largest logits, softmax over those alone."""
+    z = h @ w_router.T + bias
     val, idx = torch.topk(z, top, dim=-1)
-    wgt = torch.softmax(val, dim=-1)
+    return idx, torch.softmax(val, dim=-1)
+
+
+def moe_ff(h, w, p, mlp):
+    top = mlp["router"]["top"]
+    idx, wgt = route(h, w[p + "router"], w[p + "router.b"], top)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for j in range(top):
