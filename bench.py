@@ -461,7 +461,8 @@ COMPARE_SIZES = {
 }
 _TIMED_OPS = ("embedding", "linear", "linear_swiglu", "linear_swiglu_small", "linear_silu_mul", "linear_qkv_rope", "act_mul",
               "qk_norm_rope_kv_write", "paged_attention", "channel_decay", "linear_attention_scan", "head_norm_gate",
-              "add_rmsnorm", "add_rmsnorm_rows", "rope_table")
+              "add_rmsnorm", "add_rmsnorm_rows", "rope_table", "latent_prepare", "head_linear", "short_conv", "unit_norm",
+              "delta_rule_scan", "moe_route", "moe_experts")
 
 
 def ganidra_config_of(sz: dict) -> dict:
@@ -476,10 +477,28 @@ def ganidra_config_of(sz: dict) -> dict:
                 layers=pair * (sz["layers"] // 2), loop=dict(start=0, stop=0, times=1))
 
 
+def besavik_config_of(sz: dict) -> dict:
+    """A Besavik model at the sizes of ``sz``: lightning, latent attention, the delta mixer and latent attention again,
+    twice over; a dense feed-forward behind the lightning layers and eight experts of half its width, two per token,
+    behind the others (the same weights at work per token as the dense one)."""
+    D = sz["head_dim"]
+    lightning = dict(heads=sz["gla_heads"], dim=sz["gla_dk"], vdim=sz["gla_dv"],
+                     decay=[1.0 - 2.0 ** (-5.0 - 4.0 * h / sz["gla_heads"]) for h in range(sz["gla_heads"])])
+    latent = dict(heads=sz["heads"], dim=D, rot_dim=D // 2, vdim=D, kv_rank=D + D // 2, q_rank=sz["width"] // 2,
+                  scale=(D + D // 2) ** -0.5, rot=dict(base=500000.0, dims=D // 2))
+    delta = dict(heads=sz["gla_heads"], kv_heads=max(1, sz["gla_heads"] // 2), dim=sz["gla_dk"], vdim=sz["gla_dv"], conv=4, rank=64)
+    dense = dict(kind="dense", ff=sz["ff"], limit=7.0)
+    moe = dict(kind="moe", expert=dict(ff=sz["ff"] // 2, limit=7.0), router=dict(experts=8, top=2))
+    four = [dict(type="lightning", mixer=lightning, mlp=dense), dict(type="latent_attention", mixer=latent, mlp=moe),
+            dict(type="channel_delta", mixer=delta, mlp=moe), dict(type="latent_attention", mixer=latent, mlp=moe)]
+    return dict(architecture="Besavik", vocab=sz["vocab"], width=sz["width"], logit_scale=1.0, norm=dict(eps=1e-6),
+                layers=four * (sz["layers"] // 4))
+
+
 def compare_designs(args) -> int:
     """``--compare ganidra``: prefill and decode of a Ganidra model beside a Qwen3 model of equal sizes (random weights,
     bfloat16), and the device time of every class of operation in one eager step of each (CUDA events around every
-    call, the calls of a class added up).  Prints one JSON line."""
+    call, the calls of a class added up).  ``--compare besavik``: a Besavik model beside both.  Prints one JSON line."""
     import torch
     from qwen_engine_b200 import ops
     from qwen_engine_b200.config import preset_config_dict
@@ -586,13 +605,19 @@ def compare_designs(args) -> int:
         sz = COMPARE_SIZES[name]
         qraw = preset_config_dict(sz["preset"])
         qraw.update(num_hidden_layers=sz["layers"], vocab_size=sz["vocab"])
-        out[name] = {"sizes": sz, "ganidra": measure(config_from_dict(ganidra_config_of(sz)), "ganidra"),
-                     "qwen3": measure(config_from_dict(qraw), "qwen3")}
-        g, q = out[name]["ganidra"], out[name]["qwen3"]
-        out[name]["ganidra_over_qwen3"] = {"prefill": round(g["prefill"]["tokens_per_s"] / q["prefill"]["tokens_per_s"], 3),
-                                           "decode": round(g["decode"]["tokens_per_s"] / q["decode"]["tokens_per_s"], 3)}
+        out[name] = {"sizes": sz}
+        if args.compare == "besavik":
+            out[name]["besavik"] = measure(config_from_dict(besavik_config_of(sz)), "besavik")
+        out[name]["ganidra"] = measure(config_from_dict(ganidra_config_of(sz)), "ganidra")
+        out[name]["qwen3"] = measure(config_from_dict(qraw), "qwen3")
+        designs = [d for d in ("besavik", "ganidra", "qwen3") if d in out[name]]
+        for other in designs[1:]:
+            g, q = out[name][designs[0]], out[name][other]
+            out[name][f"{designs[0]}_over_{other}"] = {"prefill": round(g["prefill"]["tokens_per_s"] / q["prefill"]["tokens_per_s"], 3),
+                                                      "decode": round(g["decode"]["tokens_per_s"] / q["decode"]["tokens_per_s"], 3)}
     clocks.stop()
-    print(json.dumps({"metric": "prefill and decode tok/s, Ganidra beside Qwen3 at equal sizes", "impl": "ours", "n_gpus": 1,
+    title = "Besavik beside Ganidra and Qwen3" if args.compare == "besavik" else "Ganidra beside Qwen3"
+    print(json.dumps({"metric": f"prefill and decode tok/s, {title} at equal sizes", "impl": "ours", "n_gpus": 1,
                       "dtype": "bf16", "data": "synthetic: uniform random token ids, random weights N(0, 0.02) seed 2",
                       "steps": args.steps, "warmup": args.warmup, "peaks": peaks_src, "sizes": out,
                       "clocks": clocks.summary([(m_start, clocks.mark())])}))
@@ -620,9 +645,10 @@ def main() -> int:
     ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel-class timings")
     ap.add_argument("--profile", choices=["decode", "prefill"], default=None,
                     help="bracket that timed region with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
-    ap.add_argument("--compare", choices=["ganidra"], default=None,
+    ap.add_argument("--compare", choices=["ganidra", "besavik"], default=None,
                     help="instead of the default workload: prefill and decode of a Ganidra model beside a Qwen3 model of equal "
-                         "sizes, with the device time of every class of operation (one JSON line)")
+                         "sizes (besavik: a Besavik model beside both), with the device time of every class of operation "
+                         "(one JSON line)")
     ap.add_argument("--compare-size", choices=sorted(COMPARE_SIZES), default=None, help="with --compare: one size only")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -263,14 +263,12 @@ delta_rule_scan_kernel(DeltaArgs A) {
       float* o = A.out + (size_t)(row0 + ch * A.chunk) * o_ld + (size_t)head * dv + j;
       for (int t = 0; t < rows; ++t) {
         float ks0 = 0.f, ks1 = 0.f, qs0 = 0.f, qs1 = 0.f, qk0 = 0.f, qk1 = 0.f;
-        float kr[DC];
 #pragma unroll
         for (int i = 0; i < DC; i += 4) {
           const float4 q4 = *reinterpret_cast<const float4*>(r + i);
           const float4 k4 = *reinterpret_cast<const float4*>(r + row_w + i);
           const float4 g4 = *reinterpret_cast<const float4*>(r + 2 * row_w + i);
           s[i] *= g4.x; s[i + 1] *= g4.y; s[i + 2] *= g4.z; s[i + 3] *= g4.w;
-          kr[i] = k4.x; kr[i + 1] = k4.y; kr[i + 2] = k4.z; kr[i + 3] = k4.w;
           ks0 = fmaf(k4.x, s[i], ks0);     qs0 = fmaf(q4.x, s[i], qs0);     qk0 = fmaf(q4.x, k4.x, qk0);
           ks1 = fmaf(k4.y, s[i + 1], ks1); qs1 = fmaf(q4.y, s[i + 1], qs1); qk1 = fmaf(q4.y, k4.y, qk1);
           ks0 = fmaf(k4.z, s[i + 2], ks0); qs0 = fmaf(q4.z, s[i + 2], qs0); qk0 = fmaf(q4.z, k4.z, qk0);
@@ -286,7 +284,10 @@ delta_rule_scan_kernel(DeltaArgs A) {
         const float beta = rv[(VT + 3) & ~3];
         const float u = A.delta ? beta * (vj - ks) : vj;
 #pragma unroll
-        for (int i = 0; i < DC; ++i) s[i] = fmaf(kr[i], u, s[i]);
+        for (int i = 0; i < DC; i += 4) {
+          const float4 k4 = *reinterpret_cast<const float4*>(r + row_w + i);
+          s[i] = fmaf(k4.x, u, s[i]); s[i + 1] = fmaf(k4.y, u, s[i + 1]); s[i + 2] = fmaf(k4.z, u, s[i + 2]); s[i + 3] = fmaf(k4.w, u, s[i + 3]);
+        }
         if (l == 0) o[(size_t)t * o_ld] = fmaf(qk, u, qs);
         r += tok_w; rv += tok_w;
       }
@@ -299,6 +300,11 @@ delta_rule_scan_kernel(DeltaArgs A) {
   }
 }
 
+// How many threads share a column of the state (a power of two up to 32; 0: the library chooses).  Fewer threads mean
+// more key channels a thread (more independent multiply-adds between the exchanges) and fewer exchanges a token.
+static int g_dr_lanes = 0;
+extern "C" void qe_delta_rule_lanes(int lanes) { g_dr_lanes = lanes; }
+
 extern "C" int qe_delta_rule_scan(const float* q, long ldq, const float* k, long ldk, const float* v, long ldv,
                                   const float* g, long ldg, const void* beta,
                                   long ld_beta, int beta_dtype, const float* head_decay, float* state, const int* cu_q,
@@ -308,6 +314,10 @@ extern "C" int qe_delta_rule_scan(const float* q, long ldq, const float* k, long
   if (dk < 1 || dk > 1024 || dv < 1) QE_REFUSE("delta_rule_scan: key size %d must be 1..1024, value size %d positive", dk, dv);
   if (H < 1 || H > 65535 || G < 1 || H % G) QE_REFUSE("delta_rule_scan: %d heads over %d key heads", H, G);
   int DC = dk <= 16 ? 4 : dk <= 64 ? 8 : dk <= 128 ? 16 : 32;
+  if (g_dr_lanes > 0) {
+    const int want = (dk + g_dr_lanes - 1) / g_dr_lanes;
+    DC = want <= 4 ? 4 : want <= 8 ? 8 : want <= 16 ? 16 : want <= 32 ? 32 : 64;
+  }
   int L = 1;
   while (L * DC < dk) L <<= 1;
   if (L > 32) QE_REFUSE("delta_rule_scan: key size %d is too large", dk);
@@ -336,7 +346,7 @@ extern "C" int qe_delta_rule_scan(const float* q, long ldq, const float* k, long
       configured = true; \
     } \
     qe_launch(delta_rule_scan_kernel<DCC>, dim3(R, H, (dv + VT - 1) / VT), dim3(threads), smem, stream, A); } while (0)
-  switch (DC) { case 4: DRL(4); break; case 8: DRL(8); break; case 16: DRL(16); break; default: DRL(32); break; }
+  switch (DC) { case 4: DRL(4); break; case 8: DRL(8); break; case 16: DRL(16); break; case 32: DRL(32); break; default: DRL(64); break; }
 #undef DRL
   QE_CHECK_LAUNCH("delta_rule_scan");
   return 0;

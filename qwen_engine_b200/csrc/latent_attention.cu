@@ -103,10 +103,43 @@ head_linear_kernel(const T* __restrict__ x, long ldx, long ldx_h, const T* __res
   });
 }
 
+__global__ void __launch_bounds__(FP_THREADS)
+head_linear_fast_kernel(const __nv_bfloat16* __restrict__ x, long ldx, long ldx_h, const __nv_bfloat16* __restrict__ w,
+                        __nv_bfloat16* __restrict__ out, long ldo, long ldo_h, int M, int N, int K) {
+  extern __shared__ __align__(16) unsigned char fp_smem[];
+  FpAcc acc;
+  constexpr int BN = FpShape<1>::BN;
+  const int m0 = blockIdx.x * FP_BM, n0 = blockIdx.y * BN, h = blockIdx.z;
+  pdl_launch_dependents();
+  pdl_wait();
+  const __nv_bfloat16* wh = w + (size_t)h * N * K;
+  fast_tile_product<1>(fp_smem, acc, K, w,
+      [&](int r) -> const __nv_bfloat16* { return m0 + r < M ? x + (size_t)(m0 + r) * ldx + (size_t)h * ldx_h : nullptr; },
+      [&](int, int n) -> const __nv_bfloat16* { return n0 + n < N ? wh + (size_t)(n0 + n) * K : nullptr; });
+  fast_tile_for_each<1>(acc, [&](int r, int n, float v, float) {
+    if (m0 + r < M && n0 + n < N) out[(size_t)(m0 + r) * ldo + (size_t)h * ldo_h + n0 + n] = __float2bfloat16_rn(v);
+  });
+}
+
 extern "C" int qe_head_linear(const void* x, long ldx, long ldx_h, const void* w, void* out, long ldo, long ldo_h,
                               int M, int H, int N, int K, int dtype, cudaStream_t stream) {
   if (M <= 0 || H <= 0 || N <= 0) return 0;
   if (K < 1 || H > 65535) QE_REFUSE("head_linear: K = %d, %d heads", K, H);
+  if (dtype == QE_DTYPE_BF16 && K % 8 == 0 && ldx % 8 == 0 && ldx_h % 8 == 0 && (((uintptr_t)x | (uintptr_t)w) & 15) == 0) {
+    // every row on a 16-byte boundary: the pipelined kernel
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(head_linear_fast_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FP_SMEM_BYTES);
+      if (e != cudaSuccess) QE_REFUSE("head_linear: shared memory: %s", cudaGetErrorString(e));
+      configured = true;
+    }
+    dim3 fgrid((M + FP_BM - 1) / FP_BM, (N + FpShape<1>::BN - 1) / FpShape<1>::BN, H);
+    if (fgrid.y > 65535) QE_REFUSE("head_linear: N = %d is too wide", N);
+    qe_launch(head_linear_fast_kernel, fgrid, dim3(FP_THREADS), FP_SMEM_BYTES, stream, (const __nv_bfloat16*)x, ldx, ldx_h,
+              (const __nv_bfloat16*)w, (__nv_bfloat16*)out, ldo, ldo_h, M, N, K);
+    QE_CHECK_LAUNCH("head_linear");
+    return 0;
+  }
   dim3 grid((M + TP_BM - 1) / TP_BM, (N + TP_BN - 1) / TP_BN, H);
   if (grid.y > 65535) QE_REFUSE("head_linear: N = %d is too wide", N);
 #define HL(TT) qe_launch(head_linear_kernel<TT>, grid, dim3(TP_THREADS), 0, stream, (const TT*)x, ldx, ldx_h, (const TT*)w, \

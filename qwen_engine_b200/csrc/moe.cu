@@ -110,19 +110,32 @@ extern "C" int qe_moe_sort(const int* top_idx, int* offsets, int* sorted_pair, i
 }
 
 // the expert and the first sorted place of row tile `tile`: experts' tiles are numbered one expert after the other
-__device__ __forceinline__ bool moe_find_tile(const int* __restrict__ offsets, int E, int tile, int* expert, int* first, int* rows) {
+__device__ __forceinline__ bool moe_find_tile(const int* __restrict__ offsets, int E, int tile, int BM, int* expert, int* first, int* rows) {
   int seen = 0;
   for (int e = 0; e < E; ++e) {
     const int lo = offsets[e], n = offsets[e + 1] - lo;
-    const int tiles = (n + TP_BM - 1) / TP_BM;
+    const int tiles = (n + BM - 1) / BM;
     if (tile < seen + tiles) {
       const int i = tile - seen;
-      *expert = e; *first = lo + i * TP_BM; *rows = min(TP_BM, n - i * TP_BM);
+      *expert = e; *first = lo + i * BM; *rows = min(BM, n - i * BM);
       return true;
     }
     seen += tiles;
   }
   return false;
+}
+
+// the activation of a gated feed-forward on a product's float32 sums, gate and up rounded as if stored
+template <typename T>
+__device__ __forceinline__ float moe_glu(float v0, float v1, int act) {
+  const float g = to_f32(from_f32<T>(v0)), u = to_f32(from_f32<T>(v1));
+  if (act > 1) {
+    const float lim = __int_as_float(act);
+    const float gl = fminf(g, lim), ul = fminf(fmaxf(u, -lim), lim);
+    return gl / (1.f + expf(-QE_GLU_SIGMOID_SLOPE * gl)) * (ul + 1.f);
+  }
+  if (act == 1) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+  return g / (1.f + expf(-g)) * u;
 }
 
 // GLU = true: w [E, 2 I, K] (gate rows, then up rows), rows gathered from x by pair / top, out [P, I] in the compute type
@@ -138,7 +151,7 @@ moe_product_kernel(const T* __restrict__ x, const T* __restrict__ w, const int* 
   pdl_wait();
   if (threadIdx.x == 0) {
     int e = 0, first = 0, rows = 0;
-    const bool ok = moe_find_tile(offsets, E, blockIdx.x, &e, &first, &rows);
+    const bool ok = moe_find_tile(offsets, E, blockIdx.x, TP_BM, &e, &first, &rows);
     s_tile[0] = ok ? e : -1; s_tile[1] = first; s_tile[2] = rows;
   }
   __syncthreads();
@@ -156,18 +169,7 @@ moe_product_kernel(const T* __restrict__ x, const T* __restrict__ w, const int* 
     if (r >= rows || n0 + n >= N) return;
     const size_t at = (size_t)(first + r) * N + n0 + n;
     if constexpr (GLU) {
-      // gate and up are rounded as if stored, then the activation in float32, rounded once
-      const float g = to_f32(from_f32<T>(v0)), u = to_f32(from_f32<T>(v1));
-      float y;
-      if (act > 1) {
-        const float lim = __int_as_float(act);
-        const float gl = fminf(g, lim), ul = fminf(fmaxf(u, -lim), lim);
-        y = gl / (1.f + expf(-QE_GLU_SIGMOID_SLOPE * gl)) * (ul + 1.f);
-      } else if (act == 1) {
-        y = 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
-      } else {
-        y = g / (1.f + expf(-g)) * u;
-      }
+      const float y = moe_glu<T>(v0, v1, act);
       ((T*)out_)[at] = from_f32<T>(y);
     } else {
       ((float*)out_)[at] = v0;
@@ -175,11 +177,71 @@ moe_product_kernel(const T* __restrict__ x, const T* __restrict__ w, const int* 
   });
 }
 
-static int moe_tiles(int P, int E) { return (P + TP_BM - 1) / TP_BM + (E < P ? E : P); }
+// The same two products for bfloat16 rows on 16-byte boundaries, on the pipelined tile of 128 rows (tile_product.cuh).
+template <bool GLU>
+__global__ void __launch_bounds__(FP_THREADS)
+moe_product_fast_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, const int* __restrict__ offsets,
+                        const int* __restrict__ sorted_pair, void* __restrict__ out_, int E, int N, int K, int top, int act) {
+  extern __shared__ __align__(16) unsigned char fp_smem[];
+  __shared__ int s_tile[4];
+  FpAcc acc;
+  constexpr int NB = GLU ? 2 : 1;
+  constexpr int BN = FpShape<NB>::BN;
+  pdl_launch_dependents();
+  pdl_wait();
+  if (threadIdx.x == 0) {
+    int e = 0, first = 0, rows = 0;
+    const bool ok = moe_find_tile(offsets, E, blockIdx.x, FP_BM, &e, &first, &rows);
+    s_tile[0] = ok ? e : -1; s_tile[1] = first; s_tile[2] = rows;
+  }
+  __syncthreads();
+  const int e = s_tile[0], first = s_tile[1], rows = s_tile[2];
+  if (e < 0) return;
+  const int n0 = blockIdx.y * BN;
+  const __nv_bfloat16* we = w + (size_t)e * NB * N * K;
+  fast_tile_product<NB>(fp_smem, acc, K, w,
+      [&](int r) -> const __nv_bfloat16* {
+        if (r >= rows) return nullptr;
+        return GLU ? x + (size_t)(sorted_pair[first + r] / top) * K : x + (size_t)(first + r) * K;
+      },
+      [&](int m, int n) -> const __nv_bfloat16* { return n0 + n < N ? we + ((size_t)m * N + n0 + n) * K : nullptr; });
+  fast_tile_for_each<NB>(acc, [&](int r, int n, float v0, float v1) {
+    if (r >= rows || n0 + n >= N) return;
+    const size_t at = (size_t)(first + r) * N + n0 + n;
+    if constexpr (GLU) ((__nv_bfloat16*)out_)[at] = __float2bfloat16_rn(moe_glu<__nv_bfloat16>(v0, v1, act));
+    else ((float*)out_)[at] = v0;
+  });
+}
+
+static int moe_tiles(int P, int E, int BM = TP_BM) { return (P + BM - 1) / BM + (E < P ? E : P); }
+
+template <bool GLU>
+static int moe_fast_launch(const void* x, const void* w, const int* offsets, const int* sorted_pair, void* out, int P, int E, int N,
+                           int K, int top, int act, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(moe_product_fast_kernel<GLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, FP_SMEM_BYTES);
+    if (e != cudaSuccess) QE_REFUSE("moe: shared memory: %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  constexpr int BN = FpShape<GLU ? 2 : 1>::BN;
+  dim3 grid(moe_tiles(P, E, FP_BM), (N + BN - 1) / BN);
+  qe_launch(moe_product_fast_kernel<GLU>, grid, dim3(FP_THREADS), FP_SMEM_BYTES, stream, (const __nv_bfloat16*)x,
+            (const __nv_bfloat16*)w, offsets, sorted_pair, out, E, N, K, top, act);
+  return 0;
+}
+static bool moe_fast_applies(const void* x, const void* w, int K, int dtype) {
+  return dtype == QE_DTYPE_BF16 && K % 8 == 0 && (((uintptr_t)x | (uintptr_t)w) & 15) == 0;
+}
 
 extern "C" int qe_moe_gate_up(const void* x, const void* w, const int* offsets, const int* sorted_pair, void* act_out,
                               int P, int E, int I, int K, int top, int act, int dtype, cudaStream_t stream) {
   if (P <= 0) return 0;
+  if (moe_fast_applies(x, w, K, dtype)) {
+    if (int rc = moe_fast_launch<true>(x, w, offsets, sorted_pair, act_out, P, E, I, K, top, act, stream)) return rc;
+    QE_CHECK_LAUNCH("moe_gate_up");
+    return 0;
+  }
   dim3 grid(moe_tiles(P, E), (I + TP_BN - 1) / TP_BN);
 #define MP(TT) qe_launch(moe_product_kernel<TT, true>, grid, dim3(TP_THREADS), 0, stream, (const TT*)x, (const TT*)w, offsets, \
                          sorted_pair, act_out, E, I, K, top, act)
@@ -194,6 +256,11 @@ extern "C" int qe_moe_gate_up(const void* x, const void* w, const int* offsets, 
 extern "C" int qe_moe_down(const void* act_in, const void* w, const int* offsets, float* y, int P, int E, int N, int K,
                            int dtype, cudaStream_t stream) {
   if (P <= 0) return 0;
+  if (moe_fast_applies(act_in, w, K, dtype)) {
+    if (int rc = moe_fast_launch<false>(act_in, w, offsets, nullptr, (void*)y, P, E, N, K, 1, 0, stream)) return rc;
+    QE_CHECK_LAUNCH("moe_down");
+    return 0;
+  }
   dim3 grid(moe_tiles(P, E), (N + TP_BN - 1) / TP_BN);
 #define MP(TT) qe_launch(moe_product_kernel<TT, false>, grid, dim3(TP_THREADS), 0, stream, (const TT*)act_in, (const TT*)w, offsets, \
                          (const int*)nullptr, (void*)y, E, N, K, 1, 0)

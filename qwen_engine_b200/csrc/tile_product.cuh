@@ -133,3 +133,115 @@ __device__ __forceinline__ void tile_for_each(const TpAcc<T, NB>& acc, F f) {
         f(warp * 16 + g + (e >> 1) * 8, nt * 8 + 2 * c + (e & 1), acc.v[0][nt][e], NB > 1 ? acc.v[NB - 1][nt][e] : 0.f);
   }
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// The same for bfloat16 where every row lies on a 16-byte boundary and K is a multiple of 8: a tile of 128 rows by
+// one CTA of 256 threads, rows and weights copied 16 bytes at a time through a ring of four stages (cp.async, zero
+// fill for rows that are not there and beyond K), fragments by ldmatrix.  NB = 1: 128 columns of one matrix, a warp
+// owns 64 rows x 32 columns.  NB = 2: 64 columns of each of two matrices, a warp owns 64 rows x the same 16 columns
+// of both.  The order of a row's sum depends on K alone.
+// ---------------------------------------------------------------------------------------------------------
+#define FP_BM 128
+#define FP_BK 32
+#define FP_LD 40                       // bfloat16 per staged row: 32 and 16 bytes of padding (ldmatrix without conflicts)
+#define FP_STAGES 4
+#define FP_THREADS 256
+#define FP_STAGE_BYTES (2 * FP_BM * FP_LD * 2)
+#define FP_SMEM_BYTES (FP_STAGES * FP_STAGE_BYTES)
+template <int NB> struct FpShape { static constexpr int BN = NB == 1 ? 128 : 64; };
+
+__device__ __forceinline__ void fp_cp16(void* dst, const void* src, int bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n"
+               :: "r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void fp_ldmatrix4(uint32_t* r, const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+}
+
+struct FpAcc { float v[4][4][4]; };    // [16-row tile of the warp's 64 rows][8-column tile][fragment]
+
+// a_row(r): row r's K elements or nullptr; b_row(m, n): row n of matrix m or nullptr; `valid`: any mapped address
+template <int NB, typename ARow, typename BRow>
+__device__ __forceinline__ void fast_tile_product(unsigned char* smem, FpAcc& acc, int K, const void* valid, ARow a_row, BRow b_row) {
+  using bf = __nv_bfloat16;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int warp_m = warp >> 2, warp_n = warp & 3;
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc.v[i][j][e] = 0.f;
+  // a thread copies two pieces of 16 bytes of A and two of B per stage: rows tid / 4 and tid / 4 + 64, piece tid % 4
+  const int prow = tid >> 2, pk = (tid & 3) * 8;
+  constexpr int BN = FpShape<NB>::BN;
+  const bf* ap[2] = {a_row(prow), a_row(prow + 64)};
+  const bf* bp[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = prow + 64 * i;                  // staged row of B: matrix r / BN, its row r % BN
+    bp[i] = NB == 1 ? b_row(0, r) : b_row(r / BN, r % BN);
+  }
+  const int steps = (K + FP_BK - 1) / FP_BK;
+  auto issue = [&](int step) {
+    bf* sa = reinterpret_cast<bf*>(smem + (size_t)(step % FP_STAGES) * FP_STAGE_BYTES);
+    bf* sb = sa + FP_BM * FP_LD;
+    const int k = step * FP_BK + pk;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const bool a_ok = ap[i] != nullptr && k < K, b_ok = bp[i] != nullptr && k < K;
+      fp_cp16(sa + (prow + 64 * i) * FP_LD + pk, a_ok ? (const void*)(ap[i] + k) : valid, a_ok ? 16 : 0);
+      fp_cp16(sb + (prow + 64 * i) * FP_LD + pk, b_ok ? (const void*)(bp[i] + k) : valid, b_ok ? 16 : 0);
+    }
+  };
+#pragma unroll
+  for (int s = 0; s < FP_STAGES - 1; ++s) {
+    if (s < steps) issue(s);
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+  }
+  for (int step = 0; step < steps; ++step) {
+    asm volatile("cp.async.wait_group %0;\n" :: "n"(FP_STAGES - 2) : "memory");
+    __syncthreads();                              // the stage has landed for everybody; the stage refilled below was read a step ago
+    if (step + FP_STAGES - 1 < steps) issue(step + FP_STAGES - 1);
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+    const bf* sa = reinterpret_cast<const bf*>(smem + (size_t)(step % FP_STAGES) * FP_STAGE_BYTES);
+    const bf* sb = sa + FP_BM * FP_LD;
+#pragma unroll
+    for (int kk = 0; kk < FP_BK; kk += 16) {
+      uint32_t b[2][4];
+#pragma unroll
+      for (int pr = 0; pr < 2; ++pr) {
+        // two 8-column tiles: staged rows base .. base + 15; matrices (n 0-7, k 0-7), (n 0-7, k 8-15), (n 8-15, k 0-7), (n 8-15, k 8-15)
+        const int base = NB == 1 ? warp_n * 32 + pr * 16 : pr * BN + warp_n * 16;
+        const int mat = lane >> 3;
+        fp_ldmatrix4(b[pr], sb + (base + (mat >> 1) * 8 + (lane & 7)) * FP_LD + kk + (mat & 1) * 8);
+      }
+#pragma unroll
+      for (int mt = 0; mt < 4; ++mt) {
+        uint32_t a[4];
+        fp_ldmatrix4(a, sa + (warp_m * 64 + mt * 16 + (lane & 15)) * FP_LD + kk + (lane >> 4) * 8);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) tp_mma_bf16(acc.v[mt][q], a, b[q >> 1][(q & 1) * 2], b[q >> 1][(q & 1) * 2 + 1]);
+      }
+    }
+  }
+  asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+}
+
+// f(row in tile, column in tile, value of matrix 0, value of matrix 1 (NB = 2) or 0)
+template <int NB, typename F>
+__device__ __forceinline__ void fast_tile_for_each(const FpAcc& acc, F f) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
+  const int warp_m = warp >> 2, warp_n = warp & 3;
+#pragma unroll
+  for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+    for (int q = 0; q < (NB == 1 ? 4 : 2); ++q)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int row = warp_m * 64 + mt * 16 + g + (e >> 1) * 8;
+        const int col = (NB == 1 ? warp_n * 32 : warp_n * 16) + q * 8 + 2 * c + (e & 1);
+        f(row, col, acc.v[mt][q][e], NB == 1 ? 0.f : acc.v[mt][q + 2][e]);
+      }
+}
