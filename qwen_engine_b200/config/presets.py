@@ -55,6 +55,19 @@ PRESETS: dict[str, dict[str, Any]] = {
                             dict(type="gla", mixer=dict(heads=4, dim=16, vdim=32, tau=4.0, rank=8), mlp=dict(kind="dense", ff=192))],
                     loop=dict(start=0, stop=2, times=2)),
         init=dict(seed=5, std=0.08, norm_std=0.1, block_size=16)),
+    # a small model of the Besavik design: linear attention with a constant decay per head, latent attention, the gated
+    # delta rule behind short convolutions; a dense feed-forward and two mixtures of routed experts
+    "besavik-tiny": dict(
+        config=dict(architecture="Besavik", vocab=320, width=128, logit_scale=0.5, norm=dict(eps=1e-6),
+                    layers=[dict(type="lightning", mixer=dict(heads=2, dim=16, vdim=32, decay=[0.9, 0.99]),
+                                 mlp=dict(kind="dense", ff=256, limit=2.0)),
+                            dict(type="latent_attention",
+                                 mixer=dict(heads=4, dim=16, rot_dim=16, vdim=32, kv_rank=48, q_rank=32, scale=0.18,
+                                            rot=dict(base=10000.0, dims=16)),
+                                 mlp=dict(kind="moe", expert=dict(ff=64, limit=2.0), router=dict(experts=4, top=2))),
+                            dict(type="channel_delta", mixer=dict(heads=4, kv_heads=2, dim=16, vdim=32, conv=4, rank=8),
+                                 mlp=dict(kind="moe", expert=dict(ff=64, limit=2.0), router=dict(experts=4, top=2)))]),
+        init=dict(seed=7, std=0.08, norm_std=0.1, block_size=16)),
 }
 
 

@@ -22,22 +22,34 @@ template <typename T>
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const T* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
                  int* __restrict__ top_idx, float* __restrict__ top_w, int T_tokens, int W, int E, int top) {
-  extern __shared__ float zs[];                     // [warps][E]
+  extern __shared__ float route_smem[];             // the token's row [W], then its logits [E]
+  float* xs = route_smem;
+  float* z = route_smem + ((W + 3) & ~3);
   pdl_launch_dependents();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-  const int t = blockIdx.x * warps + warp;
-  if (t >= T_tokens) return;
-  float* z = zs + (size_t)warp * E;
+  const int t = blockIdx.x;
   const T* xr = x + (size_t)t * W;
-  for (int e = 0; e < E; ++e) {
+  for (int d = threadIdx.x; d < W; d += blockDim.x) xs[d] = to_f32(xr[d]);
+  __syncthreads();
+  // a warp per expert in turn; a lane's share of the row in four sums that do not wait for each other, then the lanes' sums
+  // in a fixed order: a logit's bits depend on W alone
+  for (int e = warp; e < E; e += warps) {
     const float* wr = w + (size_t)e * W;
-    float acc = 0.f;
-    for (int d = lane; d < W; d += 32) acc = fmaf(to_f32(xr[d]), wr[d], acc);
-    acc = warp_sum(acc);
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    int d = lane;
+    for (; d + 96 < W; d += 128) {
+      a0 = fmaf(xs[d], wr[d], a0);
+      a1 = fmaf(xs[d + 32], wr[d + 32], a1);
+      a2 = fmaf(xs[d + 64], wr[d + 64], a2);
+      a3 = fmaf(xs[d + 96], wr[d + 96], a3);
+    }
+    for (; d < W; d += 32) a0 = fmaf(xs[d], wr[d], a0);
+    const float acc = warp_sum((a0 + a1) + (a2 + a3));
     if (lane == 0) z[e] = acc + (bias ? bias[e] : 0.f);
   }
-  __syncwarp();
+  __syncthreads();
+  if (warp != 0) return;
   float chosen[MOE_MAX_TOP];
   float zmax = 0.f;
   for (int j = 0; j < top; ++j) {
@@ -65,10 +77,16 @@ extern "C" int qe_moe_route(const void* x, const float* w, const float* bias, in
                             int E, int top, int dtype, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (E < 1 || E > MOE_MAX_E || top < 1 || top > MOE_MAX_TOP || top > E) QE_REFUSE("moe_route: %d of %d experts", top, E);
-  const int warps = 4;
-  const size_t smem = (size_t)warps * E * sizeof(float);
-#define MR(TT) qe_launch(moe_route_kernel<TT>, dim3((T + warps - 1) / warps), dim3(warps * 32), smem, stream, (const TT*)x, w, bias, \
-                         top_idx, top_w, T, W, E, top)
+  const size_t smem = ((size_t)((W + 3) & ~3) + E) * sizeof(float);
+  if (smem > 160 * 1024) QE_REFUSE("moe_route: a row of %d channels does not fit shared memory", W);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(moe_route_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+    if (e != cudaSuccess) QE_REFUSE("moe_route: shared memory: %s", cudaGetErrorString(e));
+    configured = true;
+  }
+#define MR(TT) qe_launch(moe_route_kernel<TT>, dim3(T), dim3(128), smem, stream, (const TT*)x, w, bias, top_idx, top_w, T, W, E, top)
   if (dtype == QE_DTYPE_F32) MR(float);
   else if (dtype == QE_DTYPE_BF16) MR(__nv_bfloat16);
   else QE_REFUSE("moe_route: unknown dtype %d", dtype);
@@ -178,10 +196,13 @@ moe_product_kernel(const T* __restrict__ x, const T* __restrict__ w, const int* 
 }
 
 // The same two products for bfloat16 rows on 16-byte boundaries, on the pipelined tile of 128 rows (tile_product.cuh).
+// K may be cut into gridDim.z shares of k_share channels (GLU = false only): share z adds up its channels alone and writes
+// its sums to out + z * P * N; the combining kernel adds the shares in their order.
 template <bool GLU>
 __global__ void __launch_bounds__(FP_THREADS)
 moe_product_fast_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, const int* __restrict__ offsets,
-                        const int* __restrict__ sorted_pair, void* __restrict__ out_, int E, int N, int K, int top, int act) {
+                        const int* __restrict__ sorted_pair, void* __restrict__ out_, int E, int N, int K, int top, int act,
+                        int k_share, long share_stride) {
   extern __shared__ __align__(16) unsigned char fp_smem[];
   __shared__ int s_tile[4];
   FpAcc acc;
@@ -198,18 +219,20 @@ moe_product_fast_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16
   const int e = s_tile[0], first = s_tile[1], rows = s_tile[2];
   if (e < 0) return;
   const int n0 = blockIdx.y * BN;
-  const __nv_bfloat16* we = w + (size_t)e * NB * N * K;
-  fast_tile_product<NB>(fp_smem, acc, K, w,
+  const int k_first = blockIdx.z * k_share;
+  const int k_len = min(k_share, K - k_first);
+  const __nv_bfloat16* we = w + (size_t)e * NB * N * K + k_first;
+  fast_tile_product<NB>(fp_smem, acc, k_len, w,
       [&](int r) -> const __nv_bfloat16* {
         if (r >= rows) return nullptr;
-        return GLU ? x + (size_t)(sorted_pair[first + r] / top) * K : x + (size_t)(first + r) * K;
+        return GLU ? x + (size_t)(sorted_pair[first + r] / top) * K : x + (size_t)(first + r) * K + k_first;
       },
       [&](int m, int n) -> const __nv_bfloat16* { return n0 + n < N ? we + ((size_t)m * N + n0 + n) * K : nullptr; });
   fast_tile_for_each<NB>(acc, [&](int r, int n, float v0, float v1) {
     if (r >= rows || n0 + n >= N) return;
     const size_t at = (size_t)(first + r) * N + n0 + n;
     if constexpr (GLU) ((__nv_bfloat16*)out_)[at] = __float2bfloat16_rn(moe_glu<__nv_bfloat16>(v0, v1, act));
-    else ((float*)out_)[at] = v0;
+    else ((float*)out_)[(size_t)blockIdx.z * share_stride + at] = v0;
   });
 }
 
@@ -217,7 +240,7 @@ static int moe_tiles(int P, int E, int BM = TP_BM) { return (P + BM - 1) / BM + 
 
 template <bool GLU>
 static int moe_fast_launch(const void* x, const void* w, const int* offsets, const int* sorted_pair, void* out, int P, int E, int N,
-                           int K, int top, int act, cudaStream_t stream) {
+                           int K, int top, int act, int shares, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(moe_product_fast_kernel<GLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, FP_SMEM_BYTES);
@@ -225,9 +248,10 @@ static int moe_fast_launch(const void* x, const void* w, const int* offsets, con
     configured = true;
   }
   constexpr int BN = FpShape<GLU ? 2 : 1>::BN;
-  dim3 grid(moe_tiles(P, E, FP_BM), (N + BN - 1) / BN);
+  dim3 grid(moe_tiles(P, E, FP_BM), (N + BN - 1) / BN, shares);
+  const int k_share = shares > 1 ? ((K + shares - 1) / shares + FP_BK - 1) / FP_BK * FP_BK : K;
   qe_launch(moe_product_fast_kernel<GLU>, grid, dim3(FP_THREADS), FP_SMEM_BYTES, stream, (const __nv_bfloat16*)x,
-            (const __nv_bfloat16*)w, offsets, sorted_pair, out, E, N, K, top, act);
+            (const __nv_bfloat16*)w, offsets, sorted_pair, out, E, N, K, top, act, k_share, (long)P * N);
   return 0;
 }
 static bool moe_fast_applies(const void* x, const void* w, int K, int dtype) {
@@ -238,7 +262,7 @@ extern "C" int qe_moe_gate_up(const void* x, const void* w, const int* offsets, 
                               int P, int E, int I, int K, int top, int act, int dtype, cudaStream_t stream) {
   if (P <= 0) return 0;
   if (moe_fast_applies(x, w, K, dtype)) {
-    if (int rc = moe_fast_launch<true>(x, w, offsets, sorted_pair, act_out, P, E, I, K, top, act, stream)) return rc;
+    if (int rc = moe_fast_launch<true>(x, w, offsets, sorted_pair, act_out, P, E, I, K, top, act, 1, stream)) return rc;
     QE_CHECK_LAUNCH("moe_gate_up");
     return 0;
   }
@@ -253,14 +277,26 @@ extern "C" int qe_moe_gate_up(const void* x, const void* w, const int* offsets, 
   return 0;
 }
 
+// In how many shares the down product cuts K: one for steps of many rows; for a few rows (decoded tokens) one per 256
+// channels, up to 8, so that enough CTAs pull the weights.  A function of P's class and K alone.
+extern "C" int qe_moe_down_shares(int P, int K, int dtype) {
+  if (dtype != QE_DTYPE_BF16 || K % 8 || P > 256) return 1;
+  const int s = K / 256;
+  return s < 1 ? 1 : s > 8 ? 8 : s;
+}
+
+// y: float32 [shares, P, N] (shares as qe_moe_down_shares says, or 1), share z holding the sums over its channels
 extern "C" int qe_moe_down(const void* act_in, const void* w, const int* offsets, float* y, int P, int E, int N, int K,
-                           int dtype, cudaStream_t stream) {
+                           int shares, int dtype, cudaStream_t stream) {
   if (P <= 0) return 0;
+  if (shares < 1 || shares > 8) QE_REFUSE("moe_down: %d shares of K", shares);
   if (moe_fast_applies(act_in, w, K, dtype)) {
-    if (int rc = moe_fast_launch<false>(act_in, w, offsets, nullptr, (void*)y, P, E, N, K, 1, 0, stream)) return rc;
+    if (int rc = moe_fast_launch<false>(act_in, w, offsets, nullptr, (void*)y, P, E, N, K, 1, 0, shares, stream)) return rc;
     QE_CHECK_LAUNCH("moe_down");
     return 0;
   }
+  // (the plain kernel adds up all of K: the other shares are zeros)
+  if (shares > 1) cudaMemsetAsync(y + (size_t)P * N, 0, (size_t)(shares - 1) * P * N * sizeof(float), stream);
   dim3 grid(moe_tiles(P, E), (N + TP_BN - 1) / TP_BN);
 #define MP(TT) qe_launch(moe_product_kernel<TT, false>, grid, dim3(TP_THREADS), 0, stream, (const TT*)act_in, (const TT*)w, offsets, \
                          (const int*)nullptr, (void*)y, E, N, K, 1, 0)
@@ -274,25 +310,30 @@ extern "C" int qe_moe_down(const void* act_in, const void* w, const int* offsets
 
 template <typename T>
 __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ place_of_pair,
-                                   const float* __restrict__ top_w, T* __restrict__ out, long total, int N, int top) {
+                                   const float* __restrict__ top_w, T* __restrict__ out, long total, int N, int top,
+                                   int shares, long share_stride) {
   pdl_launch_dependents();
   pdl_wait();
   for (long e = (long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long)gridDim.x * blockDim.x) {
     const long t = e / N;
     const int n = (int)(e - t * N);
     float acc = 0.f;
-    for (int j = 0; j < top; ++j)
-      acc = fmaf(top_w[t * top + j], y[(size_t)place_of_pair[t * top + j] * N + n], acc);
+    for (int j = 0; j < top; ++j) {
+      const float* src = y + (size_t)place_of_pair[t * top + j] * N + n;
+      float v = src[0];
+      for (int z = 1; z < shares; ++z) v += src[(size_t)z * share_stride];
+      acc = fmaf(top_w[t * top + j], v, acc);
+    }
     out[e] = from_f32<T>(acc);
   }
 }
 
 extern "C" int qe_moe_combine(const float* y, const int* place_of_pair, const float* top_w, void* out, int T, int N, int top,
-                              int dtype, cudaStream_t stream) {
+                              int shares, int dtype, cudaStream_t stream) {
   if (T <= 0) return 0;
   const long total = (long)T * N;
   const unsigned blocks = (unsigned)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-#define MC(TT) qe_launch(moe_combine_kernel<TT>, dim3(blocks), dim3(256), 0, stream, y, place_of_pair, top_w, (TT*)out, total, N, top)
+#define MC(TT) qe_launch(moe_combine_kernel<TT>, dim3(blocks), dim3(256), 0, stream, y, place_of_pair, top_w, (TT*)out, total, N, top, shares, (long)T * top * N)
   if (dtype == QE_DTYPE_F32) MC(float);
   else if (dtype == QE_DTYPE_BF16) MC(__nv_bfloat16);
   else QE_REFUSE("moe_combine: unknown dtype %d", dtype);

@@ -1425,9 +1425,12 @@ def moe_experts(x: torch.Tensor, top_idx: torch.Tensor, top_w: torch.Tensor, w_g
     act = alloc((P, I), x.dtype)
     _check(lib().qe_moe_gate_up(_ptr(x), _ptr(w_gate_up), _ptr(offsets), _ptr(sorted_pair), _ptr(act), P, E, I, K, top,
                                 gate_code(activation), _dt(x), _stream()), "moe_gate_up")
-    y = alloc((P, N), torch.float32)
-    _check(lib().qe_moe_down(_ptr(act), _ptr(w_down), _ptr(offsets), _ptr(y), P, E, N, I, _dt(x), _stream()), "moe_down")
-    _check(lib().qe_moe_combine(_ptr(y), _ptr(place), _ptr(top_w), _ptr(out), T, N, top, _dt(out), _stream()), "moe_combine")
+    # a few rows (decoded tokens): the down product cuts K into shares so that enough CTAs pull the weights; the shares' sums
+    # are added, in their order, where the token's choices are
+    shares = int(lib().qe_moe_down_shares(P, I, _dt(x)))
+    y = alloc((shares, P, N), torch.float32)
+    _check(lib().qe_moe_down(_ptr(act), _ptr(w_down), _ptr(offsets), _ptr(y), P, E, N, I, shares, _dt(x), _stream()), "moe_down")
+    _check(lib().qe_moe_combine(_ptr(y), _ptr(place), _ptr(top_w), _ptr(out), T, N, top, shares, _dt(out), _stream()), "moe_combine")
 
 
 def scaled_add(acc: torch.Tensor, x: torch.Tensor, scale: float, first: bool = False) -> None:
