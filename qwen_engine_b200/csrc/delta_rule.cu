@@ -155,12 +155,12 @@ __device__ __forceinline__ void dr_cp_async16(float* dst, const float* src) {
 
 template <int DC> __device__ __forceinline__ int dr_pad(int c) { return c + (c / DC) * 4; }
 
-template <int DC>
+template <int DC, int L>
 __global__ void __launch_bounds__(DR_MAX_THREADS)
 delta_rule_scan_kernel(DeltaArgs A) {
   extern __shared__ float smem[];
   const int req = blockIdx.x, head = blockIdx.y, j0 = blockIdx.z * A.VT;
-  const int dk = A.dk, dv = A.dv, L = A.L, VT = A.VT, H = A.H;
+  const int dk = A.dk, dv = A.dv, VT = A.VT, H = A.H;
   const int grp = head / (H / A.G);
   const int padded = L * DC;
   const int row_w = dr_pad<DC>(padded);                 // floats of a staged row of q, k or g
@@ -169,7 +169,6 @@ delta_rule_scan_kernel(DeltaArgs A) {
   const int tid = threadIdx.x;
   const int j = j0 + tid / L, l = tid % L;
   const bool owns = tid < VT * L && j < dv;
-  const unsigned col_mask = L >= 32 ? 0xffffffffu : (((1u << L) - 1u) << ((tid & 31) & ~(L - 1)));
   pdl_launch_dependents();
   pdl_wait();
   const int row0 = A.cu_q[req];
@@ -199,11 +198,45 @@ delta_rule_scan_kernel(DeltaArgs A) {
     if (c >= dk) { dst[0] = 0.f; dst[row_w] = 0.f; dst[2 * row_w] = 1.f; }
     else if (!g) dst[2 * row_w] = hd;
   }
+  // Pieces of 16 bytes sit at the same places in every chunk: a thread works out once which of them are its own (the
+  // chunk's row, where from within the row, where to), and a chunk's copies are then a few instructions each.
+  constexpr int NP = 16;
+  const int pk_ = dk / 4, pv_ = VT / 4;
+  const int per_tok_v = (g ? 3 : 2) * pk_ + pv_;
+  const bool described = vec && A.chunk * per_tok_v <= NP * (int)blockDim.x;
+  int p_meta[NP], p_off[NP];                 // meta: destination (floats from the buffer's start) | kind << 20 | row << 24; -1: none
+  if (described) {
+#pragma unroll
+    for (int i = 0; i < NP; ++i) {
+      const int e = tid + i * blockDim.x;
+      p_meta[i] = -1; p_off[i] = 0;
+      if (e < A.chunk * per_tok_v) {
+        const int t = e / per_tok_v;
+        int x = e - t * per_tok_v, kind, dst;
+        if (x < pk_) { kind = 0; dst = dr_pad<DC>(x * 4); }
+        else if ((x -= pk_) < pk_) { kind = 1; dst = row_w + dr_pad<DC>(x * 4); }
+        else if (g && (x -= pk_) < pk_) { kind = 2; dst = 2 * row_w + dr_pad<DC>(x * 4); }
+        else { x -= pk_; kind = j0 + x * 4 < dv ? 3 : 4; dst = 3 * row_w + x * 4; }
+        if (kind < 4) { p_meta[i] = (t * tok_w + dst) | (kind << 20) | (t << 24); p_off[i] = x * 4; }
+      }
+    }
+  }
   auto stage = [&](int ch) {
     float* b = buf[ch & 1];
     const int t_first = ch * A.chunk;
     const int rows = min(A.chunk, n - t_first);
-    if (vec) {
+    if (described) {
+      const size_t base_row = (size_t)(row0 + t_first);
+#pragma unroll
+      for (int i = 0; i < NP; ++i) {
+        const int m = p_meta[i];
+        if (m < 0 || (m >> 24) >= rows) continue;
+        const int kind = (m >> 20) & 7;
+        const size_t row = base_row + (m >> 24);
+        const float* src = kind == 0 ? q + row * ld_q : kind == 1 ? k + row * ld_k : kind == 2 ? g + row * ld_g : v + row * ld_v;
+        dr_cp_async16(b + (m & 0xfffff), src + p_off[i]);
+      }
+    } else if (vec) {
       const int pk = dk / 4, pv = VT / 4;
       const int per_tok = (g ? 3 : 2) * pk + pv;
       for (int e = tid; e < rows * per_tok; e += blockDim.x) {
@@ -256,7 +289,10 @@ delta_rule_scan_kernel(DeltaArgs A) {
     if (ch + 1 < n_chunks) { stage(ch + 1); asm volatile("cp.async.wait_group 1;\n" ::: "memory"); }
     else asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     __syncthreads();
-    if (owns) {
+    {
+      // every thread of the CTA walks the tokens, also those whose column lies beyond the head (they keep zeros and store
+      // nothing): the exchanges below are then whole-warp ones, which a warp runs in one go; a column's L lanes are
+      // neighbours, so an exchange over distances below L stays within the column
       const int rows = min(A.chunk, n - ch * A.chunk);
       const float* r = buf[ch & 1] + l * (DC + 4);
       const float* rv = buf[ch & 1] + 3 * row_w;
@@ -275,12 +311,13 @@ delta_rule_scan_kernel(DeltaArgs A) {
           ks1 = fmaf(k4.w, s[i + 3], ks1); qs1 = fmaf(q4.w, s[i + 3], qs1); qk1 = fmaf(q4.w, k4.w, qk1);
         }
         float ks = ks0 + ks1, qs = qs0 + qs1, qk = qk0 + qk1;
+#pragma unroll
         for (int off = 1; off < L; off <<= 1) {
-          ks += __shfl_xor_sync(col_mask, ks, off);
-          qs += __shfl_xor_sync(col_mask, qs, off);
-          qk += __shfl_xor_sync(col_mask, qk, off);
+          ks += __shfl_xor_sync(0xffffffffu, ks, off);
+          qs += __shfl_xor_sync(0xffffffffu, qs, off);
+          qk += __shfl_xor_sync(0xffffffffu, qk, off);
         }
-        const float vj = rv[j - j0];
+        const float vj = rv[min(j - j0, VT - 1)];
         const float beta = rv[(VT + 3) & ~3];
         const float u = A.delta ? beta * (vj - ks) : vj;
 #pragma unroll
@@ -288,7 +325,7 @@ delta_rule_scan_kernel(DeltaArgs A) {
           const float4 k4 = *reinterpret_cast<const float4*>(r + row_w + i);
           s[i] = fmaf(k4.x, u, s[i]); s[i + 1] = fmaf(k4.y, u, s[i + 1]); s[i + 2] = fmaf(k4.z, u, s[i + 2]); s[i + 3] = fmaf(k4.w, u, s[i + 3]);
         }
-        if (l == 0) o[(size_t)t * o_ld] = fmaf(qk, u, qs);
+        if (owns && l == 0) o[(size_t)t * o_ld] = fmaf(qk, u, qs);
         r += tok_w; rv += tok_w;
       }
     }
@@ -338,15 +375,18 @@ extern "C" int qe_delta_rule_scan(const float* q, long ldq, const float* k, long
   const size_t smem = (size_t)2 * A.chunk * tok_w * sizeof(float);
   if (smem > 200 * 1024) QE_REFUSE("delta_rule_scan: key size %d needs %zu bytes of shared memory", dk, smem);
   const int threads = ((VT * L + 31) / 32) * 32;
-#define DRL(DCC) do { \
+#define DRL(DCC, LL) do { \
     static bool configured = false; \
     if (!configured) { \
-      cudaError_t e = cudaFuncSetAttribute(delta_rule_scan_kernel<DCC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+      cudaError_t e = cudaFuncSetAttribute(delta_rule_scan_kernel<DCC, LL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
       if (e != cudaSuccess) QE_REFUSE("delta_rule_scan: shared memory: %s", cudaGetErrorString(e)); \
       configured = true; \
     } \
-    qe_launch(delta_rule_scan_kernel<DCC>, dim3(R, H, (dv + VT - 1) / VT), dim3(threads), smem, stream, A); } while (0)
-  switch (DC) { case 4: DRL(4); break; case 8: DRL(8); break; case 16: DRL(16); break; case 32: DRL(32); break; default: DRL(64); break; }
+    qe_launch(delta_rule_scan_kernel<DCC, LL>, dim3(R, H, (dv + VT - 1) / VT), dim3(threads), smem, stream, A); } while (0)
+#define DRL_L(DCC) do { switch (L) { case 1: DRL(DCC, 1); break; case 2: DRL(DCC, 2); break; case 4: DRL(DCC, 4); break; \
+    case 8: DRL(DCC, 8); break; case 16: DRL(DCC, 16); break; default: DRL(DCC, 32); break; } } while (0)
+  switch (DC) { case 4: DRL_L(4); break; case 8: DRL_L(8); break; case 16: DRL_L(16); break; case 32: DRL_L(32); break; default: DRL_L(64); break; }
+#undef DRL_L
 #undef DRL
   QE_CHECK_LAUNCH("delta_rule_scan");
   return 0;

@@ -24,13 +24,17 @@ latent_prepare_kernel(const T* __restrict__ down, long ld_down, const T* __restr
                       const int* __restrict__ slot_mapping, T* __restrict__ qlat, int H, int dn, int R, int Dr,
                       int write_kv) {
   __shared__ float red[33];
+  extern __shared__ float lp_cs[];                  // the token's cosines [half], then its sines [half]
   pdl_launch_dependents();
-  pdl_wait();
   const int t = blockIdx.x;
   const int D = R + Dr;
-  const float pos = (float)positions[t];
-  const T* row = down + (size_t)t * ld_down;
   const int half = rot_dims / 2;
+  // positions and frequencies come from the host's copy and the weights: the angles are ready before the wait
+  const float pos = (float)positions[t];
+  for (int f = threadIdx.x; f < half; f += blockDim.x) sincosf(pos * inv_freq[f], &lp_cs[half + f], &lp_cs[f]);
+  pdl_wait();
+  __syncthreads();
+  const T* row = down + (size_t)t * ld_down;
   if (write_kv) {
     float ss = 0.f;
     for (int d = threadIdx.x; d < R; d += blockDim.x) { const float v = to_f32(row[d]); ss = fmaf(v, v, ss); }
@@ -43,8 +47,7 @@ latent_prepare_kernel(const T* __restrict__ down, long ld_down, const T* __restr
       float v = to_f32(row[R + i]);
       if (i < rot_dims) {
         const int f = i < half ? i : i - half;
-        float sn, cs;
-        sincosf(pos * inv_freq[f], &sn, &cs);
+        const float cs = lp_cs[f], sn = lp_cs[half + f];
         const float other = to_f32(row[R + (i < half ? i + half : i - half)]);
         v = i < half ? v * cs - other * sn : v * cs + other * sn;
       }
@@ -58,8 +61,7 @@ latent_prepare_kernel(const T* __restrict__ down, long ld_down, const T* __restr
     float v = to_f32(qr[i]);
     if (i < rot_dims) {
       const int f = i < half ? i : i - half;
-      float sn, cs;
-      sincosf(pos * inv_freq[f], &sn, &cs);
+      const float cs = lp_cs[f], sn = lp_cs[half + f];
       const float other = to_f32(qr[i < half ? i + half : i - half]);
       v = i < half ? v * cs - other * sn : v * cs + other * sn;
     }
@@ -74,7 +76,9 @@ extern "C" int qe_latent_prepare(const void* down, long ld_down, const void* q, 
   if (T <= 0) return 0;
   if (rot_dims < 0 || rot_dims > Dr || rot_dims % 2) QE_REFUSE("latent_prepare: %d rotated dimensions of %d", rot_dims, Dr);
   if (H < 1 || dn < 0 || R < 1 || Dr < 0) QE_REFUSE("latent_prepare: sizes %d %d %d %d", H, dn, R, Dr);
-#define LP(TT) qe_launch(latent_prepare_kernel<TT>, dim3(T), dim3(128), 0, stream, (const TT*)down, ld_down, (const TT*)q, ldq, \
+  const size_t lp_smem = (size_t)(rot_dims > 0 ? rot_dims : 2) * sizeof(float);
+  if (lp_smem > 40 * 1024) QE_REFUSE("latent_prepare: %d rotated dimensions", rot_dims);
+#define LP(TT) qe_launch(latent_prepare_kernel<TT>, dim3(T), dim3(128), lp_smem, stream, (const TT*)down, ld_down, (const TT*)q, ldq, \
                          norm_w, eps, positions, inv_freq, rot_dims, (TT*)cache, slot_mapping, (TT*)qlat, H, dn, R, Dr, write_kv)
   if (dtype == QE_DTYPE_F32) LP(float);
   else if (dtype == QE_DTYPE_BF16) LP(__nv_bfloat16);

@@ -557,6 +557,35 @@ __global__ void head_norm_gate_kernel(const TI* __restrict__ o, long ldo, const 
   }
 }
 
+// The same for long rows (heads joined into one, a whole projection): a CTA per (token, head), so that a step of a few
+// tokens does not leave a row of thousands of channels to one warp.
+template <typename T, typename TI>
+__global__ void __launch_bounds__(256)
+head_norm_gate_block_kernel(const TI* __restrict__ o, long ldo, const T* __restrict__ g, long ldg, const float* __restrict__ w,
+                            float eps, T* __restrict__ out, long ldout, float scale, int gate, int H, int D) {
+  __shared__ float red[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const long t = blockIdx.x / H;
+  const int h = (int)(blockIdx.x - t * H);
+  const TI* x = o + (size_t)t * ldo + (size_t)h * D;
+  float rstd = 1.f;
+  if (w) {
+    float ss = 0.f;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) { const float val = to_f32(x[d]); ss = fmaf(val, val, ss); }
+    ss = block_sum(ss, red);
+    rstd = rsqrtf(ss / (float)D + eps);
+  }
+  const T* gr = g ? g + (size_t)t * ldg + (size_t)h * D : nullptr;
+  T* dst = out + (size_t)t * ldout + (size_t)h * D;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float val = to_f32(x[d]) * rstd;
+    if (w) val *= w[d];
+    if (gr) val *= gate_value(to_f32(gr[d]), gate);
+    dst[d] = from_f32<T>(val * scale);
+  }
+}
+
 // The same for bfloat16 gates and outputs where a head is a multiple of 128 channels and everything lies on 16-byte
 // boundaries: a lane takes four neighbouring channels of every 128 (16 bytes of float32 o, 8 bytes of gate and of
 // output), all loads on their way before the sum of squares.
@@ -637,6 +666,16 @@ extern "C" int qe_head_norm_gate(const void* o, long ldo, int o_f32, const void*
     if (o_f32) { if (D == 128) HNGV(float, 1); else HNGV(float, 2); }
     else { if (D == 128) HNGV(__nv_bfloat16, 1); else HNGV(__nv_bfloat16, 2); }
 #undef HNGV
+    QE_CHECK_LAUNCH("head_norm_gate");
+    return 0;
+  }
+  if (D >= 512 && items <= 65535L * 32) {
+#define HNGB(TT, TI) qe_launch(head_norm_gate_block_kernel<TT, TI>, dim3((unsigned)items), dim3(256), 0, stream, (const TI*)o, ldo, \
+                               (const TT*)g, ldg, w, eps, (TT*)out, ldout, scale, gate, H, D)
+    if (dtype == QE_DTYPE_F32) HNGB(float, float);
+    else if (dtype == QE_DTYPE_BF16) { if (o_f32) HNGB(__nv_bfloat16, float); else HNGB(__nv_bfloat16, __nv_bfloat16); }
+    else QE_REFUSE("head_norm_gate: unknown dtype %d", dtype);
+#undef HNGB
     QE_CHECK_LAUNCH("head_norm_gate");
     return 0;
   }
