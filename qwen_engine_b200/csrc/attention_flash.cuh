@@ -322,6 +322,7 @@ __device__ __forceinline__ void flash_attention_cta(const FaArgs& A, int item_id
   }
   __syncthreads();
   const bool skip = QROWS < FA_BM && nrows > QROWS; // the launcher promised small tiles (never true)
+  const bool one_plane = A.kv_planes == 1;          // a cache whose values are the keys' channels: a tile is fetched once
   volatile int* abort_flag = &s_abort;
   // The previous kernel of the step wrote q and the keys and values of the new tokens (positions
   // from ctx on).  Key tiles that end before ctx hold only what earlier steps wrote: the fetching
@@ -376,10 +377,10 @@ __device__ __forceinline__ void flash_attention_cta(const FaArgs& A, int item_id
           else { blk = kj / page_size; off = kj - blk * page_size; }
           const __nv_bfloat16* src = head_base + (size_t)table[blk] * page_stride + off * D + ch * 8;
           cp_async16(dk + so, src);
-          cp_async16(dv + so, src + v_off);
+          if (!one_plane) cp_async16(dv + so, src + v_off);       // (one plane: the values are read where the keys landed)
         } else {
           *reinterpret_cast<uint4*>(dk + so) = make_uint4(0, 0, 0, 0);
-          *reinterpret_cast<uint4*>(dv + so) = make_uint4(0, 0, 0, 0);
+          if (!one_plane) *reinterpret_cast<uint4*>(dv + so) = make_uint4(0, 0, 0, 0);
         }
       }
       fa_bar_arrive_on_copies(&bar_full[stage]);    // when this thread's copies have landed
@@ -415,7 +416,7 @@ __device__ __forceinline__ void flash_attention_cta(const FaArgs& A, int item_id
     if (warp_active) {
       const int kt = kt_first + t * FA_BN;
       const __nv_bfloat16* tk = sk + stage * FA_BN * LD;
-      const __nv_bfloat16* tv = sv + stage * FA_BN * LD;
+      const __nv_bfloat16* tv = (one_plane ? sk : sv) + stage * FA_BN * LD;
       // whether the whole tile is allowed for all 16 rows of this warp (then no mask is needed)
       const int row_first = row_base, row_last = min(row_base + 15, nrows - 1);
       const int pos_first = first_pos + row_first / G, pos_last = first_pos + row_last / G;
