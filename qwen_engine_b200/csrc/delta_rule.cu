@@ -3,7 +3,7 @@
 //
 //   S <- diag(g_t) S;   u = beta_t (v_t - S^T k_t);   S <- S + k_t u^T;   o_t = S^T q_t
 //
-// so the read-out sees the token's own write.  A value channel's column of S evolves on its own: thread (j, l) keeps DC
+// (o is read after the token's own update).  A value channel's column of S evolves on its own: thread (j, l) keeps DC
 // consecutive key channels of column j in registers, L threads a column within one warp (as the scan of gated linear
 // attention).  Per token a column needs k.s and q.s of the decayed column; q.k is the same for all columns, and
 // o = q.s + (q.k) u, so the three sums are formed in one pass and reduced together.  The order of every sum depends on

@@ -1343,7 +1343,7 @@ def short_conv(x: torch.Tensor, w: torch.Tensor, state: torch.Tensor, ctx, out: 
                silu: bool = True) -> None:
     """A short causal convolution over the tokens of each request, channel by channel, then silu:
     out[t, c] = silu(sum_j w[c, j] x[t - (taps - 1) + j, c]).  x [T, C] in the compute type (rows may be strided);
-    w float32 [C, taps], the last column is the current token's; state float32 [slots, taps - 1, C] holds each
+    w float32 [C, taps], tap taps - 1 multiplies the token itself; state float32 [slots, taps - 1, C] holds each
     request's last taps - 1 inputs (zeros count for a request without context) and is moved on; out float32 [T, C]."""
     _rows(x, "short_conv: x")
     T, C = x.shape

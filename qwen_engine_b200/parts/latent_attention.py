@@ -11,7 +11,7 @@ of R channels:
 The rotation turns the pairs (x[i], x[i + dims/2]) of the first ``dims`` rotated channels by position x base^(-2i/dims).
 The joined heads are multiplied by sigmoid(W_g h) and projected by W_o.
 
-Only c and the rotated k_rot are cached (one plane of R + dr channels per token).  W_uk is folded into the query
+The cache holds c and the rotated k_rot, one plane of R + dr channels per token and nothing per head.  W_uk is folded into the query
 (q_lat,h = W_uk,h^T q_plain,h) and W_uv applied after the softmax, so the paged attention kernels see ONE key/value
 head of R + dr channels whose values are the keys' first R channels, for prompt portions and decoded tokens alike.
 Norms, angles, scores and softmax are float32.

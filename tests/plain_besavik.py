@@ -94,7 +94,7 @@ def lightning(h, w, p, m, eps):
 
 
 def short_conv(x, taps_w):
-    """x [T, C]; taps_w [C, taps], the last column is the current token's; zeros before the start."""
+    """x [T, C]; taps_w [C, taps]: tap taps - 1 multiplies the token itself, and inputs before the first token count as zero."""
     T, C = x.shape
     taps = taps_w.shape[1]
     padded = torch.cat([torch.zeros(taps - 1, C, dtype=x.dtype), x], dim=0)
