@@ -117,7 +117,7 @@ head_linear_fast_kernel(const __nv_bfloat16* __restrict__ x, long ldx, long ldx_
   pdl_launch_dependents();
   pdl_wait();
   const __nv_bfloat16* wh = w + (size_t)h * N * K;
-  fast_tile_product<1>(fp_smem, acc, K, w,
+  fast_tile_product<1>(fp_smem, acc, K, w, min(FP_BM, M - m0),
       [&](int r) -> const __nv_bfloat16* { return m0 + r < M ? x + (size_t)(m0 + r) * ldx + (size_t)h * ldx_h : nullptr; },
       [&](int, int n) -> const __nv_bfloat16* { return n0 + n < N ? wh + (size_t)(n0 + n) * K : nullptr; });
   fast_tile_for_each<1>(acc, [&](int r, int n, float v, float) {

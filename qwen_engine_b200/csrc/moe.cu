@@ -222,7 +222,7 @@ moe_product_fast_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16
   const int k_first = blockIdx.z * k_share;
   const int k_len = min(k_share, K - k_first);
   const __nv_bfloat16* we = w + (size_t)e * NB * N * K + k_first;
-  fast_tile_product<NB>(fp_smem, acc, k_len, w,
+  fast_tile_product<NB>(fp_smem, acc, k_len, w, rows,
       [&](int r) -> const __nv_bfloat16* {
         if (r >= rows) return nullptr;
         return GLU ? x + (size_t)(sorted_pair[first + r] / top) * K : x + (size_t)(first + r) * K + k_first;

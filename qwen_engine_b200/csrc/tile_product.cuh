@@ -161,9 +161,39 @@ __device__ __forceinline__ void fp_ldmatrix4(uint32_t* r, const void* p) {
 
 struct FpAcc { float v[4][4][4]; };    // [16-row tile of the warp's 64 rows][8-column tile][fragment]
 
-// a_row(r): row r's K elements or nullptr; b_row(m, n): row n of matrix m or nullptr; `valid`: any mapped address
+// One staged step of 32 channels for a warp: its 64 rows x four 8-column tiles.  FULL: all four 16-row tiles hold rows;
+// otherwise only the first `tiles` of them do and the others are left out (the same for all lanes of the warp).
+template <int NB, bool FULL>
+__device__ __forceinline__ void fp_stage_mma(const __nv_bfloat16* sa, const __nv_bfloat16* sb, FpAcc& acc, int warp_m, int warp_n,
+                                             int lane, int tiles) {
+  constexpr int BN = FpShape<NB>::BN;
+#pragma unroll
+  for (int kk = 0; kk < FP_BK; kk += 16) {
+    uint32_t b[2][4];
+#pragma unroll
+    for (int pr = 0; pr < 2; ++pr) {
+      // two 8-column tiles: staged rows base .. base + 15; matrices (n 0-7, k 0-7), (n 0-7, k 8-15), (n 8-15, k 0-7), (n 8-15, k 8-15)
+      const int base = NB == 1 ? warp_n * 32 + pr * 16 : pr * BN + warp_n * 16;
+      const int mat = lane >> 3;
+      fp_ldmatrix4(b[pr], sb + (base + (mat >> 1) * 8 + (lane & 7)) * FP_LD + kk + (mat & 1) * 8);
+    }
+#pragma unroll
+    for (int mt = 0; mt < 4; ++mt) {
+      if (!FULL && mt >= tiles) break;
+      uint32_t a[4];
+      fp_ldmatrix4(a, sa + (warp_m * 64 + mt * 16 + (lane & 15)) * FP_LD + kk + (lane >> 4) * 8);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) tp_mma_bf16(acc.v[mt][q], a, b[q >> 1][(q & 1) * 2], b[q >> 1][(q & 1) * 2 + 1]);
+    }
+  }
+}
+
+// a_row(r): row r's K elements or nullptr; b_row(m, n): row n of matrix m or nullptr; `valid`: any mapped address;
+// `rows`: rows of the tile that are there (the first ones): a warp multiplies only its 16-row tiles that hold any, so a
+// tile of a few rows (a decode step) costs its weights' copies and little else
 template <int NB, typename ARow, typename BRow>
-__device__ __forceinline__ void fast_tile_product(unsigned char* smem, FpAcc& acc, int K, const void* valid, ARow a_row, BRow b_row) {
+__device__ __forceinline__ void fast_tile_product(unsigned char* smem, FpAcc& acc, int K, const void* valid, int rows, ARow a_row,
+                                                  BRow b_row) {
   using bf = __nv_bfloat16;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int warp_m = warp >> 2, warp_n = warp & 3;
@@ -184,6 +214,7 @@ __device__ __forceinline__ void fast_tile_product(unsigned char* smem, FpAcc& ac
     bp[i] = NB == 1 ? b_row(0, r) : b_row(r / BN, r % BN);
   }
   const int steps = (K + FP_BK - 1) / FP_BK;
+  const int my_tiles = min(4, max(0, (rows - warp_m * 64 + 15) / 16));     // of this warp's four 16-row tiles
   auto issue = [&](int step) {
     bf* sa = reinterpret_cast<bf*>(smem + (size_t)(step % FP_STAGES) * FP_STAGE_BYTES);
     bf* sb = sa + FP_BM * FP_LD;
@@ -207,24 +238,8 @@ __device__ __forceinline__ void fast_tile_product(unsigned char* smem, FpAcc& ac
     asm volatile("cp.async.commit_group;\n" ::: "memory");
     const bf* sa = reinterpret_cast<const bf*>(smem + (size_t)(step % FP_STAGES) * FP_STAGE_BYTES);
     const bf* sb = sa + FP_BM * FP_LD;
-#pragma unroll
-    for (int kk = 0; kk < FP_BK; kk += 16) {
-      uint32_t b[2][4];
-#pragma unroll
-      for (int pr = 0; pr < 2; ++pr) {
-        // two 8-column tiles: staged rows base .. base + 15; matrices (n 0-7, k 0-7), (n 0-7, k 8-15), (n 8-15, k 0-7), (n 8-15, k 8-15)
-        const int base = NB == 1 ? warp_n * 32 + pr * 16 : pr * BN + warp_n * 16;
-        const int mat = lane >> 3;
-        fp_ldmatrix4(b[pr], sb + (base + (mat >> 1) * 8 + (lane & 7)) * FP_LD + kk + (mat & 1) * 8);
-      }
-#pragma unroll
-      for (int mt = 0; mt < 4; ++mt) {
-        uint32_t a[4];
-        fp_ldmatrix4(a, sa + (warp_m * 64 + mt * 16 + (lane & 15)) * FP_LD + kk + (lane >> 4) * 8);
-#pragma unroll
-        for (int q = 0; q < 4; ++q) tp_mma_bf16(acc.v[mt][q], a, b[q >> 1][(q & 1) * 2], b[q >> 1][(q & 1) * 2 + 1]);
-      }
-    }
+    if (my_tiles == 4) fp_stage_mma<NB, true>(sa, sb, acc, warp_m, warp_n, lane, 4);
+    else if (my_tiles > 0) fp_stage_mma<NB, false>(sa, sb, acc, warp_m, warp_n, lane, my_tiles);
   }
   asm volatile("cp.async.wait_group 0;\n" ::: "memory");
 }
