@@ -55,6 +55,7 @@ latent_prepare_kernel(const T* __restrict__ down, long ld_down, const T* __restr
     }
   }
   // every head's rotated query part, behind the room for its folded plain part
+#pragma unroll 4
   for (int e = threadIdx.x; e < H * Dr; e += blockDim.x) {
     const int h = e / Dr, i = e - h * Dr;
     const T* qr = q + (size_t)t * ldq + (size_t)h * (dn + Dr) + dn;

@@ -34,6 +34,7 @@ channel_decay_kernel(const T* __restrict__ a, long lda, const T* __restrict__ w,
   float* as = ws + DEC_COLS * (R + 1);       // [DEC_ROWS][R]
   const int n0 = blockIdx.x * DEC_COLS, t0 = blockIdx.y * DEC_ROWS;
   pdl_launch_dependents();
+#pragma unroll 8
   for (int e = threadIdx.x; e < DEC_COLS * R; e += blockDim.x) {       // weights: nothing of the step writes them
     const int n = e / R, r = e - n * R;
     ws[n * (R + 1) + r] = n0 + n < N ? to_f32(w[(size_t)(n0 + n) * R + r]) : 0.f;
@@ -572,12 +573,14 @@ head_norm_gate_block_kernel(const TI* __restrict__ o, long ldo, const T* __restr
   float rstd = 1.f;
   if (w) {
     float ss = 0.f;
+#pragma unroll 4
     for (int d = threadIdx.x; d < D; d += blockDim.x) { const float val = to_f32(x[d]); ss = fmaf(val, val, ss); }
     ss = block_sum(ss, red);
     rstd = rsqrtf(ss / (float)D + eps);
   }
   const T* gr = g ? g + (size_t)t * ldg + (size_t)h * D : nullptr;
   T* dst = out + (size_t)t * ldout + (size_t)h * D;
+#pragma unroll 4
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
     float val = to_f32(x[d]) * rstd;
     if (w) val *= w[d];
