@@ -51,7 +51,7 @@ BESAVIK = {
         _layer("latent_attention", _latent(1, 16, 16, 32, 16, 8, 0.15, 500.0, dims=8), _moe(3, 1, 16, 2.0)),
         _layer("lightning", _lightning(4, 8, 8, (0.99, 0.7, 0.3, 1.0)), _dense(64, 0.5)),
         _layer("channel_delta", _delta(2, 2, 16, 16, 2, 7), _moe(4, 4, 32, 1.0)),
-        _layer("latent_attention", _latent(2, 24, 8, 16, 24, 16, 0.3, 100.0), None)]), seed=5, std=0.1, norm_std=0.1, page=16),
+        _layer("latent_attention", _latent(2, 24, 8, 16, 40, 16, 0.3, 100.0), None)]), seed=5, std=0.1, norm_std=0.1, page=16),
     # sizes that are no multiples of four, one key head for three heads, convolutions of five taps and of one
     "b-c": dict(cfg=_model(97, 40, 2.0, 3e-6, [
         _layer("lightning", _lightning(1, 10, 6, (0.8,)), _moe(2, 1, 12, 3.0)),
@@ -65,6 +65,15 @@ BESAVIK = {
         _layer("channel_delta", _delta(4, 2, 128, 64, 4, 16), _moe(8, 2, 64, 1.2)),
         _layer("latent_attention", _latent(8, 32, 64, 32, 64, 48, 0.1, 500000.0), _dense(256, 1.0))]),
         seed=13, std=0.05, norm_std=0.1, page=16),
+    # no attention at all: nothing is paged
+    "b-e": dict(cfg=_model(150, 48, 1.5, 1e-6, [
+        _layer("channel_delta", _delta(2, 1, 8, 8, 4, 4), _dense(64, 1.0)),
+        _layer("lightning", _lightning(3, 8, 16, (0.9, 0.95, 0.5)), _moe(4, 2, 16, 1.0))]), seed=17, std=0.12, norm_std=0.2, page=16),
+    # attention alone, of two sizes (two groups of pages): no state of fixed size, so equal prefixes share pages
+    "b-f": dict(cfg=_model(180, 64, 0.7, 1e-6, [
+        _layer("latent_attention", _latent(2, 16, 16, 16, 32, 24, 0.2, 1000.0), _dense(96, 2.0)),
+        _layer("latent_attention", _latent(4, 8, 8, 8, 24, 16, 0.25, 1000.0), _moe(4, 2, 24, 1.0)),
+        _layer("latent_attention", _latent(2, 16, 16, 16, 32, 24, 0.2, 1000.0), None)]), seed=19, std=0.12, norm_std=0.2, page=8),
 }
 
 

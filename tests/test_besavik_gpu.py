@@ -545,3 +545,21 @@ def test_the_command_line_replays_a_trace(folders, tmp_path):
     last = torch.frombuffer(bytearray((out / "2.f32").read_bytes()), dtype=F32).reshape(-1, V)
     bh.assert_close_rows(first, want[[0, 20]], F32, "step 0")
     bh.assert_close_rows(last, torch.stack([want[29], want[3]]), F32, "step 2")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_alone_shares_the_pages_of_equal_prefixes(folders, dtype):
+    """A model of latent attention alone keeps no state of fixed size, so a second request with the same first tokens takes
+    the first one's pages in both groups of pages (a prompt found whole gets a private copy of its last page)."""
+    name = "b-f"
+    folder = folders[name]
+    V = bh.vocab_of(name)
+    first = random_tokens(V, 40, 5)
+    second = first[:24] + random_tokens(V, 10, 6)
+    rep = bh.make_replayer(folder, name, dtype, 256)
+    assert rep.cache.prefix_cache and len(rep.cache.paged_groups) == 2
+    steps = [{"entries": [{"id": "a", "tokens": first, "want": [39]}]},
+             {"entries": [{"id": "b", "tokens": second, "want": [30, 33]}, {"id": "c", "tokens": first, "want": [39]}], "end": ["a", "b", "c"]}]
+    got = run_steps(rep, steps)
+    assert rep.cache.prefix_hit_tokens == 24 + 39
+    bh.check_requests(got, folder, {"a": first, "b": second, "c": first}, dtype, "shared prefix")

@@ -19,7 +19,7 @@ F32 = torch.float32
 @pytest.fixture(scope="module")
 def folders(tmp_path_factory):
     root = tmp_path_factory.mktemp("besavik")
-    return {name: bh.make_folder(str(root / name), name) for name in ("b-a", "b-b", "b-c")}
+    return {name: bh.make_folder(str(root / name), name) for name in ("b-a", "b-b", "b-c", "b-e", "b-f")}
 
 
 def test_config_reads_its_own_keys_and_round_trips():
@@ -76,7 +76,7 @@ def test_tensor_names_and_the_ranks_that_no_key_names(folders):
         check_against_manifest(src, build_model(config_from_dict(raw)).weight_manifest(), "folder")
 
 
-@pytest.mark.parametrize("name", ["b-a", "b-b", "b-c"])
+@pytest.mark.parametrize("name", ["b-a", "b-b", "b-c", "b-e", "b-f"])
 def test_replay_on_the_host(folders, cpu_ops, name):
     folder = folders[name]
     bh.replay_cases(lambda n: bh.make_replayer(folder, name, F32, n, device="cpu", poison=True), folder, name, F32,
@@ -96,3 +96,21 @@ def test_greedy_generation_through_the_engine_on_the_host(folders, cpu_ops):
     for rid, p in zip(ids, prompts):
         assert list(outs[rid].output_token_ids) == plain_besavik.greedy(cfg, w, p, 6), f"prompt of {len(p)} tokens"
     assert eng.cache.slots.num_free == eng.cache.slots.num_slots
+
+
+def test_attention_alone_shares_the_pages_of_equal_prefixes(folders, cpu_ops):
+    """A model without state of fixed size shares prefixes: a second request with the same first tokens takes the first
+    one's pages (of both groups of pages) and its logits are the plain model's all the same."""
+    from helpers import run_steps
+    name = "b-f"
+    folder = folders[name]
+    V = bh.vocab_of(name)
+    first = random_tokens(V, 40, 5)
+    second = first[:24] + random_tokens(V, 10, 6)
+    rep = bh.make_replayer(folder, name, F32, 192, device="cpu")
+    assert rep.cache.prefix_cache and len(rep.cache.paged_groups) == 2
+    steps = [{"entries": [{"id": "a", "tokens": first, "want": [39]}]},
+             {"entries": [{"id": "b", "tokens": second, "want": [30, 33]}], "end": ["a", "b"]}]
+    got = run_steps(rep, steps)
+    assert rep.cache.prefix_hit_tokens == 24
+    bh.check_requests(got, folder, {"a": first, "b": second}, F32, "shared prefix")
