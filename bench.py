@@ -485,7 +485,7 @@ def besavik_config_of(sz: dict) -> dict:
     lightning = dict(heads=sz["gla_heads"], dim=sz["gla_dk"], vdim=sz["gla_dv"],
                      decay=[1.0 - 2.0 ** (-5.0 - 4.0 * h / sz["gla_heads"]) for h in range(sz["gla_heads"])])
     latent = dict(heads=sz["heads"], dim=D, rot_dim=D // 2, vdim=D, kv_rank=D + D // 2, q_rank=sz["width"] // 2,
-                  scale=(D + D // 2) ** -0.5, rot=dict(base=500000.0, dims=D // 2))
+                  scale=(D + D // 2) ** -0.5, rot=dict(base=1000000.0, dims=D // 2))
     delta = dict(heads=sz["gla_heads"], kv_heads=max(1, sz["gla_heads"] // 2), dim=sz["gla_dk"], vdim=sz["gla_dv"], conv=4, rank=64)
     dense = dict(kind="dense", ff=sz["ff"], limit=7.0)
     moe = dict(kind="moe", expert=dict(ff=sz["ff"] // 2, limit=7.0), router=dict(experts=8, top=2))

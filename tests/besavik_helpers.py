@@ -59,11 +59,11 @@ BESAVIK = {
         _layer("latent_attention", _latent(2, 6, 4, 10, 10, 7, 0.4, 50.0), _moe(6, 3, 20, 0.7)),
         _layer("channel_delta", _delta(2, 2, 12, 4, 1, 2))]), seed=9, std=0.15, norm_std=0.3, page=8),
     # sizes of real heads: a cache row of 128 channels (the kernels' fast paths), 128 key channels in the delta mixer
-    "b-d": dict(cfg=_model(513, 256, 0.25, 1e-6, [
+    "b-d": dict(cfg=_model(513, 256, 0.3, 1e-6, [
         _layer("lightning", _lightning(2, 64, 128, (0.95, 0.999)), _dense(384, 1.0)),
-        _layer("latent_attention", _latent(8, 32, 64, 32, 64, 48, 0.1, 500000.0), _moe(8, 3, 128, 1.0)),
-        _layer("channel_delta", _delta(4, 2, 128, 64, 4, 16), _moe(8, 2, 64, 1.2)),
-        _layer("latent_attention", _latent(8, 32, 64, 32, 64, 48, 0.1, 500000.0), _dense(256, 1.0))]),
+        _layer("latent_attention", _latent(8, 32, 64, 32, 64, 48, 0.1, 200000.0), _moe(8, 3, 128, 1.0)),
+        _layer("channel_delta", _delta(4, 2, 128, 64, 4, 16), _moe(8, 2, 96, 1.2)),
+        _layer("latent_attention", _latent(8, 32, 64, 32, 64, 48, 0.1, 200000.0), _dense(256, 1.0))]),
         seed=13, std=0.05, norm_std=0.1, page=16),
     # no attention at all: nothing is paged
     "b-e": dict(cfg=_model(150, 48, 1.5, 1e-6, [
